@@ -1,0 +1,223 @@
+/*
+ * sddmm_b200 -- C ABI of the B200 (sm_100a) SDDMM engine.
+ *
+ *     P[i] = ( sum_{t<K} W[row_i*K + t] * H[col_i*K + t] ) [ * S.val_i ]
+ *
+ * for every nonzero i of a row-sorted sparse matrix S (M x N, COO, 0-based
+ * int32 indices), W (M x K) and H (N x K) dense, row-major, fp32.  P is returned
+ * in the order of the input nonzeros.
+ *
+ * Every entry point is a drop-in for one piece of the reference program
+ * (isratnisa/SDDMM_GPU); the piece is cited above each declaration by its path
+ * inside that project.  Plain pointers and sizes only: no C++ types cross this
+ * boundary, nothing throws or aborts, every function returns a status code.
+ *
+ * A handle is bound to one CUDA device and is used by one host thread at a time
+ * (the reference is single-threaded, HiPC18/src/sddmm.cu:32-151).  For several
+ * GPUs run one handle per device (one process per GPU) and split S with
+ * sddmm_partition_rows().
+ */
+#ifndef SDDMM_B200_H
+#define SDDMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SDDMM_API __attribute__((visibility("default")))
+
+/* ---- status codes -------------------------------------------------------- */
+enum {
+    SDDMM_OK = 0,
+    SDDMM_INVALID_ARG = 1,        /* NULL pointer, negative size, bad flag        */
+    SDDMM_UNSORTED_INPUT = 2,     /* rows[] not non-decreasing                     */
+    SDDMM_INDEX_OUT_OF_RANGE = 3, /* a row >= M or col >= N or negative index      */
+    SDDMM_K_UNSUPPORTED = 4,      /* K <= 0, K % 4 != 0 or K > SDDMM_MAX_K         */
+    SDDMM_CUDA_ERROR = 5,         /* see sddmm_last_error()                        */
+    SDDMM_NCCL_ERROR = 6,
+    SDDMM_OUT_OF_MEMORY = 7,
+    SDDMM_DEVICE_TIMEOUT = 8,     /* a bounded device-side wait gave up            */
+    SDDMM_IO_ERROR = 9,           /* file missing / unreadable / unwritable        */
+    SDDMM_PARSE_ERROR = 10,       /* malformed Matrix Market text                  */
+    SDDMM_NO_DEVICE = 11          /* no CUDA device: there is no CPU fallback      */
+};
+
+#define SDDMM_MAX_K 4096
+
+/* ---- execute flags ------------------------------------------------------- */
+#define SDDMM_FLAG_ASYNC        0x1u /* return after enqueue on the handle's stream (device pointers only) */
+#define SDDMM_FLAG_TILED_ORDER  0x2u /* P in the plan's tiled order (what the reference's sddmm_GPU leaves in d_val, sddmm.cu:119) instead of input order */
+#define SDDMM_FLAG_KERNEL_GATHER 0x10u /* force the planless gather kernel */
+#define SDDMM_FLAG_KERNEL_PANEL  0x20u /* force the TMA-staged row-panel kernel */
+
+/* ---- plan flags ---------------------------------------------------------- */
+#define SDDMM_PLAN_SKIP_VALIDATION 0x1u /* trust sortedness and bounds (the reference checks neither) */
+#define SDDMM_PLAN_DEVICE_INDICES  0x2u /* rows/cols are device pointers on the handle's device */
+
+typedef struct sddmm_handle_s *sddmm_handle_t;
+typedef struct sddmm_plan_s *sddmm_plan_t;
+
+/* Human-readable name of a status code (static storage). */
+SDDMM_API const char *sddmm_status_string(int status);
+
+/*
+ * Replaces the implicit "device 0, fresh allocations and streams on every call"
+ * set-up of sddmm_GPU (HiPC18/src/sddmm.cu:38-46,78-84).  Creates the compute
+ * stream and the timing events once.  SDDMM_NO_DEVICE when no GPU is usable.
+ */
+SDDMM_API int sddmm_create(sddmm_handle_t *out, int device);
+SDDMM_API int sddmm_destroy(sddmm_handle_t h);
+
+/* Text of the last CUDA / parse error seen through this handle ("" if none). */
+SDDMM_API const char *sddmm_last_error(sddmm_handle_t h);
+
+/*
+ * Run on a caller-owned CUDA stream (a cudaStream_t passed as void*) instead of
+ * the handle's own; NULL restores the handle's stream.  The reference launches
+ * on its private stream[0] (sddmm.cu:81-84,102).
+ */
+SDDMM_API int sddmm_set_stream(sddmm_handle_t h, void *cuda_stream);
+
+/*
+ * Replaces make_CSR (HiPC18/src/util.h:131-153), the TiledMatrix constructor
+ * (util.h:52-65), rewrite_matrix_1D (util.h:267-343) and the index uploads of
+ * sddmm_GPU (sddmm.cu:41-64): validates the row-sorted COO (unless told not to),
+ * copies the indices to the device once and runs the GPU binning pass (row
+ * pointer over ALL rows -- empty rows are fine -- row-panel work items, and, when
+ * col_tile_hint < N, the column-tile permutation).
+ *
+ *   panel_rows_hint : the CLI's argv[3] (rows of W per shared-memory panel,
+ *                     "tile_sizeY"/actv_row_size in the reference, sddmm.cu:253-255);
+ *                     clamped to what fits the sm_100a shared memory for this K;
+ *                     <= 0 lets the engine choose.
+ *   col_tile_hint   : the CLI's argv[4] (column-tile width, "tile_sizeX",
+ *                     sddmm.cu:254); >= N or <= 0 means a single column tile,
+ *                     i.e. the identity permutation.
+ * The plan is reusable for any number of sddmm_execute() calls.
+ */
+SDDMM_API int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz,
+                             const int32_t *rows, const int32_t *cols, int K,
+                             int panel_rows_hint, int col_tile_hint, uint32_t flags,
+                             sddmm_plan_t *out);
+SDDMM_API int sddmm_destroy_plan(sddmm_plan_t p);
+
+/*
+ * Replaces the W/H uploads, cudaMemset, launch loop and result download of
+ * sddmm_GPU (HiPC18/src/sddmm.cu:53,71-73,93-119) and the kernel comp_kernel_COO
+ * (HiPC18/src/kernel.h:2-52) -- one launch, no K-slicing.
+ *
+ *   W, H, P : host or device pointers (detected); host buffers are copied
+ *             through plan-owned device staging inside the call.
+ *   Sval    : NULL -> the unscaled dot product, as sddmm_CPU_COO and the
+ *             reference kernel store it (sddmm.cu:192, kernel.h:48);
+ *             else P[i] *= Sval[i], as sddmm_CPU_CSR does (sddmm.cu:171).
+ * Synchronous unless SDDMM_FLAG_ASYNC (the reference waits on its stop event,
+ * sddmm.cu:110).
+ */
+SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
+                            const float *Sval, float *P, uint32_t flags);
+
+/* Milliseconds of the kernels of the last synchronous sddmm_execute(), measured
+ * with CUDA events on the compute stream -- the region the reference times and
+ * prints as "Time for SDDMM with K = ..." (sddmm.cu:93,109-114). */
+SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
+
+/*
+ * One-shot form with the shape of the reference's sddmm_GPU(S, tS, P, W, H)
+ * (HiPC18/src/sddmm.cu:32): all pointers host or device, nothing is kept between
+ * calls, no plan.  Uses the planless gather kernel.
+ */
+SDDMM_API int sddmm_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz,
+                        const int32_t *rows, const int32_t *cols, const float *Sval,
+                        const float *W, const float *H, int K, float *P);
+
+/* Sizes of what the binning pass built (test and reporting hook). */
+typedef struct {
+    int64_t M, N, nnz;
+    int32_t K;
+    int32_t panel_rows;     /* rows of W per staged panel actually used        */
+    int32_t col_tile;       /* column-tile width actually used (N if single)   */
+    int32_t n_col_tiles;
+    int64_t n_work_items;
+    int64_t n_nonempty_rows;
+    int64_t n_nonempty_cols; /* -1 unless computed (sddmm_plan_count_cols)     */
+    int64_t device_bytes;   /* device memory the plan owns                     */
+    float plan_ms;          /* device time of the binning pass                 */
+} sddmm_plan_info;
+SDDMM_API int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info);
+
+/* Number of distinct columns of S (N_nz of the algorithmic-bytes formula);
+ * computed on the device on request and cached in the plan. */
+SDDMM_API int sddmm_plan_count_cols(sddmm_plan_t p, int64_t *n_nonempty_cols);
+
+/* Row pointer over all M rows (M + 1 int64 entries, host buffer), the GPU
+ * replacement of make_CSR's row_ptr/row_holder pair (util.h:131-153). */
+SDDMM_API int sddmm_plan_export_row_ptr(sddmm_plan_t p, int64_t *row_ptr);
+
+/*
+ * Test hook: the tables rewrite_matrix_1D (HiPC18/src/util.h:267-343) would
+ * produce for the same (panel_rows, col_tile), computed by the GPU binning pass,
+ * in the reference's layout and sizes (TiledMatrix constructor, util.h:52-65):
+ *   t_rows, t_cols, tiled_ind : nnz each
+ *   lastIdx_tile              : ntile_c + 1,              ntile_c = N/col_tile + 1
+ *   lastIdx_block_tile        : (ntile_c + 1) * max_blk,  max_blk = M/panel_rows + 1
+ *   active_row                : M * ntile_c
+ *   n_actv_row                : ntile_c
+ * All host buffers; any of them may be NULL to skip it.  panel_rows/col_tile are
+ * the CLI's argv[3]/argv[4] taken literally (not clamped).
+ */
+SDDMM_API int sddmm_plan_export_tiling(sddmm_plan_t p, int panel_rows, int col_tile,
+                                       int32_t *t_rows, int32_t *t_cols,
+                                       int32_t *tiled_ind, int32_t *lastIdx_tile,
+                                       int32_t *lastIdx_block_tile, int32_t *active_row,
+                                       int32_t *n_actv_row, int32_t *max_active_row);
+
+/*
+ * Replaces the nnz-balanced cuts of make_CSC (HiPC18_mpi/util.h:100-135), over
+ * ROWS instead of columns: cuts[g] .. cuts[g+1] is the row range of part g
+ * (n_parts + 1 entries, cuts[0] = 0, cuts[n_parts] = M), each cut the first
+ * multiple of align_rows whose prefix holds >= g*nnz/n_parts nonzeros.
+ * nnz_cuts (n_parts + 1) receives the matching nonzero offsets.  Pure host code.
+ */
+SDDMM_API int sddmm_partition_rows(int64_t M, int64_t nnz, const int32_t *rows,
+                                   int n_parts, int align_rows, int64_t *cuts,
+                                   int64_t *nnz_cuts);
+
+/* ---- Matrix Market I/O (host) -------------------------------------------- */
+
+/*
+ * Replaces the loader in main (HiPC18/src/sddmm.cu:257-281): skips the banner
+ * and comment lines, reads "M N nnz", then nnz triples "row col val" (1-based).
+ * Accepts everything the reference accepts; additionally accepts a size line that
+ * is the first line and `pattern` files (value 1.0), expands `symmetric` only on
+ * request, and reports what the reference silently mis-parses as
+ * SDDMM_PARSE_ERROR.  Two-call protocol: sddmm_mtx_open reads the file and
+ * reports the sizes, sddmm_mtx_read copies into caller buffers and closes.
+ */
+typedef struct sddmm_mtx_s *sddmm_mtx_t;
+SDDMM_API int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N,
+                             int64_t *nnz, char *errbuf, int errbuf_len);
+SDDMM_API int sddmm_mtx_read(sddmm_mtx_t f, int32_t *rows, int32_t *cols, float *vals);
+SDDMM_API int sddmm_mtx_close(sddmm_mtx_t f);
+/* 0/1: whether the triples just read are sorted by row (what the engine needs). */
+SDDMM_API int sddmm_coo_is_row_sorted(int64_t nnz, const int32_t *rows);
+SDDMM_API int sddmm_mtx_write(const char *path, int64_t M, int64_t N, int64_t nnz,
+                              const int32_t *rows, const int32_t *cols, const float *vals);
+
+/*
+ * Replaces unsorted_make_CSR (HiPC18/src/util.h:82-128), the README's "conversion
+ * code from col sorted to row sorted".  In place, 0-based in and out.
+ *   transpose = 1 : the reference's live behaviour -- sort by (col,row,val) and
+ *                   swap the roles, i.e. emit S^T row-sorted; *M and *N swap.
+ *   transpose = 0 : stable sort by (row, col) of S itself (the commented variant,
+ *                   util.h:93).
+ */
+SDDMM_API int sddmm_coo_sort_rows(int64_t *M, int64_t *N, int64_t nnz, int32_t *rows,
+                                  int32_t *cols, float *vals, int transpose);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SDDMM_B200_H */

@@ -1,0 +1,291 @@
+"""ctypes binding of ``libsddmm_b200.so`` -- the C ABI declared in
+``include/sddmm_b200.h``.
+
+This is the host-side mirror a Python caller uses; it adds nothing to the C ABI
+except argument marshalling.  Pointers may be numpy arrays (host), torch tensors
+(host or CUDA) or raw integer addresses.  There is no CPU fallback: without the
+built library (or without a GPU, for the compute calls) everything here raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libsddmm_b200.so")
+
+# status codes (include/sddmm_b200.h)
+OK, INVALID_ARG, UNSORTED_INPUT, INDEX_OUT_OF_RANGE, K_UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, \
+    OUT_OF_MEMORY, DEVICE_TIMEOUT, IO_ERROR, PARSE_ERROR, NO_DEVICE = range(12)
+
+FLAG_ASYNC = 0x1
+FLAG_TILED_ORDER = 0x2
+FLAG_KERNEL_GATHER = 0x10
+FLAG_KERNEL_PANEL = 0x20
+PLAN_SKIP_VALIDATION = 0x1
+PLAN_DEVICE_INDICES = 0x2
+
+EXPORTED_SYMBOLS = [
+    "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
+    "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_coo",
+    "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_plan_export_row_ptr",
+    "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_mtx_open", "sddmm_mtx_read",
+    "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
+]
+
+
+class SddmmError(RuntimeError):
+    def __init__(self, status, detail=""):
+        self.status = status
+        msg = lib().sddmm_status_string(status).decode()
+        super().__init__(f"sddmm status {status} ({msg})" + (f": {detail}" if detail else ""))
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [("M", C.c_int64), ("N", C.c_int64), ("nnz", C.c_int64), ("K", C.c_int32),
+                ("panel_rows", C.c_int32), ("col_tile", C.c_int32), ("n_col_tiles", C.c_int32),
+                ("n_work_items", C.c_int64), ("n_nonempty_rows", C.c_int64),
+                ("n_nonempty_cols", C.c_int64), ("device_bytes", C.c_int64), ("plan_ms", C.c_float)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `make -C sddmm_gpu_b200/csrc` "
+            "(or __graft_entry__.build()).  There is no CPU fallback.")
+    L = C.CDLL(LIB_PATH)
+    vp, i64, i32, u32 = C.c_void_p, C.c_int64, C.c_int32, C.c_uint32
+    L.sddmm_status_string.restype = C.c_char_p
+    L.sddmm_status_string.argtypes = [C.c_int]
+    L.sddmm_create.argtypes = [C.POINTER(vp), C.c_int]
+    L.sddmm_destroy.argtypes = [vp]
+    L.sddmm_last_error.restype = C.c_char_p
+    L.sddmm_last_error.argtypes = [vp]
+    L.sddmm_set_stream.argtypes = [vp, vp]
+    L.sddmm_plan_coo.argtypes = [vp, i64, i64, i64, vp, vp, C.c_int, C.c_int, C.c_int, u32, C.POINTER(vp)]
+    L.sddmm_destroy_plan.argtypes = [vp]
+    L.sddmm_execute.argtypes = [vp, vp, vp, vp, vp, u32]
+    L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    L.sddmm_coo.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, vp]
+    L.sddmm_plan_get_info.argtypes = [vp, C.POINTER(PlanInfo)]
+    L.sddmm_plan_count_cols.argtypes = [vp, C.POINTER(i64)]
+    L.sddmm_plan_export_row_ptr.argtypes = [vp, vp]
+    L.sddmm_plan_export_tiling.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, vp, vp, vp, vp, C.POINTER(i32)]
+    L.sddmm_partition_rows.argtypes = [i64, i64, vp, C.c_int, C.c_int, vp, vp]
+    L.sddmm_mtx_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
+                                 C.c_char_p, C.c_int]
+    L.sddmm_mtx_read.argtypes = [vp, vp, vp, vp]
+    L.sddmm_mtx_close.argtypes = [vp]
+    L.sddmm_coo_is_row_sorted.argtypes = [i64, vp]
+    L.sddmm_mtx_write.argtypes = [C.c_char_p, i64, i64, i64, vp, vp, vp]
+    L.sddmm_coo_sort_rows.argtypes = [C.POINTER(i64), C.POINTER(i64), i64, vp, vp, vp, C.c_int]
+    for name in EXPORTED_SYMBOLS:
+        fn = getattr(L, name)
+        if fn.restype is C.c_int or fn.restype is None:
+            fn.restype = C.c_int
+    _lib = L
+    return L
+
+
+def _ptr(a):
+    """Address of a numpy array / torch tensor / int / None."""
+    if a is None:
+        return None
+    if isinstance(a, int):
+        return a
+    if isinstance(a, np.ndarray):
+        if not a.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):  # torch tensor
+        if not a.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return a.data_ptr()
+    raise TypeError(f"cannot take the address of {type(a)}")
+
+
+class Handle:
+    """One engine instance bound to one CUDA device (sddmm_create)."""
+
+    def __init__(self, device=0):
+        self._h = C.c_void_p()
+        st = lib().sddmm_create(C.byref(self._h), device)
+        if st != OK:
+            self._h = None
+            raise SddmmError(st)
+        self.device = device
+
+    def close(self):
+        if self._h:
+            lib().sddmm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def last_error(self):
+        return lib().sddmm_last_error(self._h).decode()
+
+    def _check(self, st):
+        if st != OK:
+            raise SddmmError(st, self.last_error())
+
+    def set_stream(self, cuda_stream):
+        """cuda_stream: integer cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream) or None."""
+        self._check(lib().sddmm_set_stream(self._h, cuda_stream))
+
+    def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, col_tile_hint=0, flags=0, nnz=None):
+        if nnz is None:
+            nnz = int(rows.shape[0])
+        is_dev = hasattr(rows, "is_cuda") and rows.is_cuda
+        if is_dev:
+            flags |= PLAN_DEVICE_INDICES
+        p = C.c_void_p()
+        st = lib().sddmm_plan_coo(self._h, M, N, nnz, _ptr(rows), _ptr(cols), K, panel_rows_hint, col_tile_hint,
+                                  flags, C.byref(p))
+        self._check(st)
+        keep = (rows, cols) if is_dev else None  # device indices are borrowed, keep them alive
+        return Plan(self, p, nnz, keep)
+
+    def sddmm_coo(self, M, N, rows, cols, W, H, K, P, Sval=None, nnz=None):
+        if nnz is None:
+            nnz = int(rows.shape[0])
+        self._check(lib().sddmm_coo(self._h, M, N, nnz, _ptr(rows), _ptr(cols), _ptr(Sval), _ptr(W), _ptr(H), K,
+                                    _ptr(P)))
+
+
+class Plan:
+    """A binned sparsity pattern, reusable across executes (sddmm_plan_coo)."""
+
+    def __init__(self, handle, p, nnz, keep):
+        self.handle = handle
+        self._p = p
+        self.nnz = nnz
+        self._keep = keep
+
+    def close(self):
+        if self._p:
+            lib().sddmm_destroy_plan(self._p)
+            self._p = None
+
+    def __del__(self):
+        try:
+            if self.handle._h:
+                self.close()
+        except Exception:
+            pass
+
+    def execute(self, W, H, P, Sval=None, flags=0):
+        self.handle._check(lib().sddmm_execute(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P), flags))
+
+    def last_kernel_ms(self):
+        ms = C.c_float()
+        self.handle._check(lib().sddmm_last_kernel_ms(self._p, C.byref(ms)))
+        return ms.value
+
+    def info(self):
+        inf = PlanInfo()
+        self.handle._check(lib().sddmm_plan_get_info(self._p, C.byref(inf)))
+        return inf
+
+    def count_cols(self):
+        n = C.c_int64()
+        self.handle._check(lib().sddmm_plan_count_cols(self._p, C.byref(n)))
+        return n.value
+
+    def export_row_ptr(self):
+        inf = self.info()
+        out = np.empty(inf.M + 1, np.int64)
+        self.handle._check(lib().sddmm_plan_export_row_ptr(self._p, out.ctypes.data))
+        return out
+
+    def export_tiling(self, panel_rows, col_tile):
+        inf = self.info()
+        M, N, nnz = inf.M, inf.N, inf.nnz
+        ntile_c = N // col_tile + 1
+        max_blk = M // panel_rows + 1
+        out = dict(
+            rows=np.zeros(nnz, np.int32), cols=np.zeros(nnz, np.int32), tiled_ind=np.zeros(nnz, np.int32),
+            lastIdx_tile=np.zeros(ntile_c + 1, np.int32),
+            lastIdx_block_tile=np.zeros((ntile_c + 1) * max_blk, np.int32),
+            active_row=np.zeros(M * ntile_c, np.int32), n_actv_row=np.zeros(ntile_c, np.int32))
+        mar = C.c_int32()
+        st = lib().sddmm_plan_export_tiling(
+            self._p, panel_rows, col_tile, out["rows"].ctypes.data, out["cols"].ctypes.data,
+            out["tiled_ind"].ctypes.data, out["lastIdx_tile"].ctypes.data,
+            out["lastIdx_block_tile"].ctypes.data, out["active_row"].ctypes.data,
+            out["n_actv_row"].ctypes.data, C.byref(mar))
+        self.handle._check(st)
+        out["max_active_row"] = mar.value
+        out["ntile_c"] = ntile_c
+        out["max_active_block"] = max_blk
+        return out
+
+
+# ---- host-only helpers (no GPU needed) -------------------------------------
+
+def partition_rows(M, rows, n_parts, align_rows=1):
+    rows = np.ascontiguousarray(rows, np.int32)
+    cuts = np.zeros(n_parts + 1, np.int64)
+    nnz_cuts = np.zeros(n_parts + 1, np.int64)
+    st = lib().sddmm_partition_rows(M, rows.shape[0], rows.ctypes.data, n_parts, align_rows, cuts.ctypes.data,
+                                    nnz_cuts.ctypes.data)
+    if st != OK:
+        raise SddmmError(st)
+    return cuts, nnz_cuts
+
+
+def mtx_read(path):
+    """Returns (M, N, rows, cols, vals) with 0-based int32 indices."""
+    f = C.c_void_p()
+    M, N, nnz = C.c_int64(), C.c_int64(), C.c_int64()
+    err = C.create_string_buffer(256)
+    st = lib().sddmm_mtx_open(os.fsencode(path), C.byref(f), C.byref(M), C.byref(N), C.byref(nnz), err, 256)
+    if st != OK:
+        raise SddmmError(st, err.value.decode())
+    rows = np.empty(nnz.value, np.int32)
+    cols = np.empty(nnz.value, np.int32)
+    vals = np.empty(nnz.value, np.float32)
+    st = lib().sddmm_mtx_read(f, rows.ctypes.data, cols.ctypes.data, vals.ctypes.data)
+    if st != OK:
+        raise SddmmError(st)
+    return M.value, N.value, rows, cols, vals
+
+
+def mtx_write(path, M, N, rows, cols, vals=None):
+    rows = np.ascontiguousarray(rows, np.int32)
+    cols = np.ascontiguousarray(cols, np.int32)
+    if vals is not None:
+        vals = np.ascontiguousarray(vals, np.float32)
+    st = lib().sddmm_mtx_write(os.fsencode(path), M, N, rows.shape[0], rows.ctypes.data, cols.ctypes.data,
+                               _ptr(vals))
+    if st != OK:
+        raise SddmmError(st)
+
+
+def coo_is_row_sorted(rows):
+    rows = np.ascontiguousarray(rows, np.int32)
+    return bool(lib().sddmm_coo_is_row_sorted(rows.shape[0], rows.ctypes.data))
+
+
+def coo_sort_rows(M, N, rows, cols, vals, transpose=False):
+    """Returns (M, N, rows, cols, vals) row-sorted; transpose=True emits S^T as the reference's converter does."""
+    rows = np.ascontiguousarray(rows, np.int32).copy()
+    cols = np.ascontiguousarray(cols, np.int32).copy()
+    vals = np.ascontiguousarray(vals, np.float32).copy()
+    m, n = C.c_int64(M), C.c_int64(N)
+    st = lib().sddmm_coo_sort_rows(C.byref(m), C.byref(n), rows.shape[0], rows.ctypes.data, cols.ctypes.data,
+                                   vals.ctypes.data, int(transpose))
+    if st != OK:
+        raise SddmmError(st)
+    return m.value, n.value, rows, cols, vals

@@ -1,0 +1,442 @@
+// GPU binning pass (see binning.cuh).  Plan-time code: runs once per sparsity
+// pattern, outside the timed SDDMM region, exactly like the host preprocessing it
+// replaces (HiPC18/src/sddmm.cu:203-233 is untimed in the reference too).
+// Scans, selections and the stable tile sort use CUB device primitives; the
+// passes that are specific to this engine are the kernels below.
+#include "binning.cuh"
+
+#include <cub/cub.cuh>
+#include <thrust/iterator/counting_iterator.h>
+#include <thrust/iterator/transform_iterator.h>
+
+#include <climits>
+#include <vector>
+
+namespace sddmm {
+
+cudaError_t Scratch::reserve(size_t n)
+{
+    if (n <= bytes) return cudaSuccess;
+    release();
+    cudaError_t e = cudaMalloc(&ptr, n);
+    if (e == cudaSuccess) bytes = n;
+    else ptr = nullptr;
+    return e;
+}
+void Scratch::release()
+{
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+}
+
+namespace {
+
+constexpr int TPB = 256;
+inline unsigned grid_for(int64_t n, int64_t cap = 148 * 32)
+{
+    int64_t b = (n + TPB - 1) / TPB;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (unsigned)b;
+}
+
+__global__ void validate_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
+                                int64_t M, int64_t N, unsigned long long *out /* [2] */)
+{
+    unsigned long long bad_sort = ULLONG_MAX, bad_range = ULLONG_MAX;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = rows[i], c = cols[i];
+        if (r < 0 || r >= M || c < 0 || c >= N) bad_range = min(bad_range, (unsigned long long)i);
+        if (i > 0 && rows[i - 1] > r) bad_sort = min(bad_sort, (unsigned long long)i);
+    }
+    if (bad_sort != ULLONG_MAX) atomicMin(&out[0], bad_sort);
+    if (bad_range != ULLONG_MAX) atomicMin(&out[1], bad_range);
+}
+
+// One thread per boundary i in [0, nnz]: rows (rows[i-1], rows[i]] start at i.
+__global__ void row_ptr_kernel(const int32_t *__restrict__ rows, int64_t nnz, int64_t M,
+                               int64_t *__restrict__ row_ptr, unsigned long long *nonempty)
+{
+    unsigned long long heads = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t prev = (i == 0) ? -1 : rows[i - 1];
+        const int64_t cur = (i == nnz) ? M : rows[i];
+        for (int64_t r = prev + 1; r <= cur; ++r) row_ptr[r] = i;
+        if (i < nnz && cur != prev) heads++;
+    }
+    // block-level sum, one atomic per warp
+    for (int o = 16; o; o >>= 1) heads += __shfl_xor_sync(0xffffffffu, heads, o);
+    if ((threadIdx.x & 31) == 0 && heads) atomicAdd(nonempty, heads);
+}
+
+__global__ void mark_cols_kernel(const int32_t *__restrict__ cols, int64_t nnz, unsigned char *mark)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x)
+        mark[cols[i]] = 1;
+}
+__global__ void count_marks_kernel(const unsigned char *__restrict__ mark, int64_t n, unsigned long long *out)
+{
+    unsigned long long c = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        c += mark[i];
+    for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0 && c) atomicAdd(out, c);
+}
+
+__global__ void tile_key_kernel(const int32_t *__restrict__ cols, int64_t nnz, int col_tile, uint32_t *keys,
+                                int32_t *idx)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        keys[i] = (uint32_t)(cols[i] / col_tile);
+        idx[i] = (int32_t)i;
+    }
+}
+__global__ void gather2_kernel(const int32_t *__restrict__ perm, const int32_t *__restrict__ a,
+                               const int32_t *__restrict__ b, int64_t nnz, int32_t *a_out, int32_t *b_out)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t p = perm[i];
+        a_out[i] = a[p];
+        b_out[i] = b[p];
+    }
+}
+
+// A nonzero opens a run when it is the first one or when its column tile or its
+// row panel differs from its predecessor's.
+struct RunHead {
+    const int32_t *rows, *cols;
+    int panel_rows, col_tile;
+    __device__ __forceinline__ bool operator()(int j) const
+    {
+        if (j == 0) return true;
+        return (rows[j] / panel_rows != rows[j - 1] / panel_rows) || (cols[j] / col_tile != cols[j - 1] / col_tile);
+    }
+};
+struct RunHeadCount {
+    RunHead h;
+    __device__ __forceinline__ int operator()(int j) const { return h(j) ? 1 : 0; }
+};
+
+__global__ void pieces_per_run_kernel(const int32_t *__restrict__ run_start, int n_runs, int item_nnz,
+                                      int64_t *pieces)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i <= n_runs; i += gridDim.x * blockDim.x) {
+        if (i == n_runs) { pieces[i] = 0; continue; }
+        const int len = run_start[i + 1] - run_start[i];
+        pieces[i] = (len + item_nnz - 1) / item_nnz;
+    }
+}
+
+// One thread per work item: find its run, cut the run into equal pieces.
+__global__ void fill_items_kernel(const int32_t *__restrict__ run_start, const int64_t *__restrict__ item_off,
+                                  int n_runs, int64_t n_items, const int32_t *__restrict__ rows, WorkItem *items)
+{
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_items; t += (int64_t)gridDim.x * blockDim.x) {
+        int lo = 0, hi = n_runs;  // last run with item_off[run] <= t
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (item_off[mid] <= t) lo = mid; else hi = mid;
+        }
+        const int64_t c = t - item_off[lo];
+        const int64_t n_i = item_off[lo + 1] - item_off[lo];
+        const int64_t s = run_start[lo], len = run_start[lo + 1] - s;
+        const int64_t b = s + (len * c) / n_i, e = s + (len * (c + 1)) / n_i;
+        WorkItem w;
+        w.nnz_begin = b;
+        w.nnz_count = (int32_t)(e - b);
+        w.row_begin = rows[b];
+        w.n_rows = rows[e - 1] - w.row_begin + 1;
+        w.reserved = 0;
+        items[t] = w;
+    }
+}
+
+#define CK(x)                         \
+    do {                              \
+        cudaError_t _e = (x);         \
+        if (_e != cudaSuccess) return _e; \
+    } while (0)
+
+}  // namespace
+
+cudaError_t validate_coo(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
+                         ValidationResult *host_out, cudaStream_t stream)
+{
+    unsigned long long init[2] = {ULLONG_MAX, ULLONG_MAX}, res[2];
+    Scratch s;
+    CK(s.reserve(sizeof(init)));
+    CK(cudaMemcpyAsync(s.ptr, init, sizeof(init), cudaMemcpyHostToDevice, stream));
+    if (nnz > 0)
+        validate_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_rows, d_cols, nnz, M, N, (unsigned long long *)s.ptr);
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(res, s.ptr, sizeof(res), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    host_out->first_unsorted = res[0] == ULLONG_MAX ? LLONG_MAX : (long long)res[0];
+    host_out->first_out_of_range = res[1] == ULLONG_MAX ? LLONG_MAX : (long long)res[1];
+    return cudaSuccess;
+}
+
+cudaError_t build_row_ptr(const int32_t *d_rows, int64_t nnz, int64_t M, int64_t *d_row_ptr,
+                          unsigned long long *d_nonempty, cudaStream_t stream)
+{
+    CK(cudaMemsetAsync(d_nonempty, 0, sizeof(unsigned long long), stream));
+    row_ptr_kernel<<<grid_for(nnz + 1), TPB, 0, stream>>>(d_rows, nnz, M, d_row_ptr, d_nonempty);
+    return cudaGetLastError();
+}
+
+cudaError_t count_distinct_cols(const int32_t *d_cols, int64_t nnz, int64_t N, int64_t *host_out,
+                                cudaStream_t stream)
+{
+    Scratch s;
+    const size_t mark_bytes = ((size_t)N + 15) & ~(size_t)15;
+    CK(s.reserve(mark_bytes + 16));
+    CK(cudaMemsetAsync(s.ptr, 0, mark_bytes + 16, stream));
+    unsigned char *mark = (unsigned char *)s.ptr;
+    unsigned long long *cnt = (unsigned long long *)(mark + mark_bytes);
+    if (nnz > 0) mark_cols_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols, nnz, mark);
+    count_marks_kernel<<<grid_for(N), TPB, 0, stream>>>(mark, N, cnt);
+    CK(cudaGetLastError());
+    unsigned long long h = 0;
+    CK(cudaMemcpyAsync(&h, cnt, sizeof(h), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    *host_out = (int64_t)h;
+    return cudaSuccess;
+}
+
+cudaError_t build_tiled_order(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t N, int col_tile,
+                              int32_t *d_perm, int32_t *d_rows_t, int32_t *d_cols_t, cudaStream_t stream)
+{
+    if (nnz == 0) return cudaSuccess;
+    const int64_t n_tiles = N / col_tile + 1;
+    int bits = 1;
+    while (((int64_t)1 << bits) < n_tiles) ++bits;
+    Scratch keys;  // keys_in | keys_out | idx_in
+    CK(keys.reserve(sizeof(uint32_t) * 3 * (size_t)nnz));
+    uint32_t *k_in = (uint32_t *)keys.ptr, *k_out = k_in + nnz;
+    int32_t *i_in = (int32_t *)(k_out + nnz);
+    tile_key_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols, nnz, col_tile, k_in, i_in);
+    CK(cudaGetLastError());
+    size_t tmp_bytes = 0;
+    CK(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, k_in, k_out, i_in, d_perm, (int)nnz, 0, bits, stream));
+    Scratch tmp;
+    CK(tmp.reserve(tmp_bytes));
+    CK(cub::DeviceRadixSort::SortPairs(tmp.ptr, tmp_bytes, k_in, k_out, i_in, d_perm, (int)nnz, 0, bits, stream));
+    gather2_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_perm, d_rows, d_cols, nnz, d_rows_t, d_cols_t);
+    CK(cudaGetLastError());
+    return cudaStreamSynchronize(stream);
+}
+
+cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, int64_t nnz, int panel_rows,
+                             int col_tile, int item_nnz, WorkItem **d_items, int64_t *n_items,
+                             cudaStream_t stream)
+{
+    *d_items = nullptr;
+    *n_items = 0;
+    if (nnz == 0) return cudaSuccess;
+    const int n = (int)nnz;
+    RunHead head{d_rows_p, d_cols_p, panel_rows, col_tile};
+    thrust::counting_iterator<int> counting(0);
+
+    // 1. number of runs
+    auto ones = thrust::make_transform_iterator(counting, RunHeadCount{head});
+    Scratch small;  // [0] n_runs (int), [8] select count (int)
+    CK(small.reserve(64));
+    int *d_n_runs = (int *)small.ptr, *d_n_sel = d_n_runs + 2;
+    size_t tmp_bytes = 0;
+    CK(cub::DeviceReduce::Sum(nullptr, tmp_bytes, ones, d_n_runs, n, stream));
+    Scratch tmp;
+    CK(tmp.reserve(tmp_bytes));
+    CK(cub::DeviceReduce::Sum(tmp.ptr, tmp_bytes, ones, d_n_runs, n, stream));
+    int n_runs = 0;
+    CK(cudaMemcpyAsync(&n_runs, d_n_runs, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+
+    // 2. run starts (+ sentinel nnz)
+    Scratch runs;  // run_start int32[n_runs+1] | pieces int64[n_runs+1] | item_off int64[n_runs+1]
+    const size_t rs_bytes = (sizeof(int32_t) * ((size_t)n_runs + 1) + 15) & ~(size_t)15;
+    const size_t pc_bytes = sizeof(int64_t) * ((size_t)n_runs + 1);
+    CK(runs.reserve(rs_bytes + 2 * pc_bytes));
+    int32_t *run_start = (int32_t *)runs.ptr;
+    int64_t *pieces = (int64_t *)((char *)runs.ptr + rs_bytes);
+    int64_t *item_off = pieces + (n_runs + 1);
+    tmp_bytes = 0;
+    CK(cub::DeviceSelect::If(nullptr, tmp_bytes, counting, run_start, d_n_sel, n, head, stream));
+    CK(tmp.reserve(tmp_bytes));
+    CK(cub::DeviceSelect::If(tmp.ptr, tmp_bytes, counting, run_start, d_n_sel, n, head, stream));
+    CK(cudaMemcpyAsync(run_start + n_runs, &n, sizeof(int), cudaMemcpyHostToDevice, stream));
+
+    // 3. pieces per run -> item offsets
+    pieces_per_run_kernel<<<grid_for(n_runs + 1), TPB, 0, stream>>>(run_start, n_runs, item_nnz, pieces);
+    CK(cudaGetLastError());
+    tmp_bytes = 0;
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, pieces, item_off, n_runs + 1, stream));
+    CK(tmp.reserve(tmp_bytes));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tmp_bytes, pieces, item_off, n_runs + 1, stream));
+    int64_t total = 0;
+    CK(cudaMemcpyAsync(&total, item_off + n_runs, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+
+    // 4. the items
+    WorkItem *items = nullptr;
+    CK(cudaMalloc(&items, sizeof(WorkItem) * (size_t)total));
+    fill_items_kernel<<<grid_for(total), TPB, 0, stream>>>(run_start, item_off, n_runs, total, d_rows_p, items);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+        cudaFree(items);
+        return e;
+    }
+    *d_items = items;
+    *n_items = total;
+    return cudaSuccess;
+}
+
+
+// ---------------------------------------------------------------------------
+// Reference-layout tiling tables (test hook)
+// ---------------------------------------------------------------------------
+namespace {
+
+// Head of a (column tile, row) segment in tiled order.
+__global__ void seg_flag_kernel(const int32_t *__restrict__ rows_t, const int32_t *__restrict__ cols_t, int64_t nnz,
+                                int col_tile, int32_t *flag)
+{
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nnz; j += (int64_t)gridDim.x * blockDim.x)
+        flag[j] = (j == 0 || rows_t[j] != rows_t[j - 1] || cols_t[j] / col_tile != cols_t[j - 1] / col_tile) ? 1 : 0;
+}
+
+// tile_begin[t] = first tiled index whose tile id is >= t, for t in [0, n_slots).
+__global__ void tile_begin_kernel(const int32_t *__restrict__ cols_t, int64_t nnz, int col_tile, int n_slots,
+                                  int32_t *tile_begin)
+{
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n_slots; t += gridDim.x * blockDim.x) {
+        int64_t lo = 0, hi = nnz;
+        while (lo < hi) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (cols_t[mid] / col_tile < t) lo = mid + 1; else hi = mid;
+        }
+        tile_begin[t] = (int32_t)lo;
+    }
+}
+
+// Per nonzero: tile-local active-row index; per segment: active_row entry and
+// block-table entries; per tile: number of active rows.
+__global__ void tiling_tables_kernel(const int32_t *__restrict__ rows_t, const int32_t *__restrict__ cols_t,
+                                     const int32_t *__restrict__ flag, const int32_t *__restrict__ segid,
+                                     const int32_t *__restrict__ tile_begin, int64_t nnz, int64_t M, int col_tile,
+                                     int panel_rows, int64_t max_blk, int32_t *t_rows, int32_t *active_row,
+                                     int32_t *block_table, int32_t *n_actv_row)
+{
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nnz; j += (int64_t)gridDim.x * blockDim.x) {
+        const int T = cols_t[j] / col_tile;
+        const int32_t tb = tile_begin[T], te = tile_begin[T + 1];
+        const int32_t a = segid[j] - segid[tb];  // inclusive scan: the tile's first segment has local index 0
+        if (t_rows) t_rows[j] = a;
+        if (flag[j] && active_row) active_row[(int64_t)T * M + a] = rows_t[j];
+        const bool seg_tail = (j + 1 == nnz) || flag[j + 1];
+        if (seg_tail) {
+            const bool last_in_tile = (j + 1 == te);
+            if (block_table) {
+                if ((a + 1) % panel_rows == 0) block_table[(int64_t)T * max_blk + (a + 1) / panel_rows - 1] = (int32_t)(j + 1);
+                else if (last_in_tile) block_table[(int64_t)T * max_blk + (a + 1) / panel_rows] = (int32_t)(j + 1);
+            }
+            if (last_in_tile && n_actv_row) n_actv_row[T] = a + 1;
+        }
+    }
+}
+
+// The reference writes slot 0 of the NEXT tile's block table at the start of
+// every tile with the current tile's start index (util.h:289-292).
+__global__ void block_table_prewrite_kernel(const int32_t *__restrict__ tile_begin, int n_loop, int64_t max_blk,
+                                            int32_t *block_table)
+{
+    for (int T = blockIdx.x * blockDim.x + threadIdx.x; T < n_loop; T += gridDim.x * blockDim.x)
+        block_table[(int64_t)(T + 1) * max_blk] = (T == 0) ? 0 : tile_begin[T];
+}
+
+}  // namespace
+
+cudaError_t export_reference_tiling(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
+                                    int panel_rows, int col_tile, const TilingTables &out, cudaStream_t stream)
+{
+    const int64_t ntile_c = N / col_tile + 1;
+    const int64_t n_loop = (N + col_tile - 1) / col_tile;  // tiles the reference loop visits
+    const int64_t max_blk = M / panel_rows + 1;
+    const size_t n = (size_t)(nnz > 0 ? nnz : 1);
+
+    Scratch idx;  // perm | rows_t | cols_t | flag | segid | local row ids
+    CK(idx.reserve(sizeof(int32_t) * 6 * n));
+    int32_t *perm = (int32_t *)idx.ptr, *rows_t = perm + n, *cols_t = rows_t + n, *flag = cols_t + n, *segid = flag + n;
+    int32_t *lrow = segid + n;
+    CK(build_tiled_order(d_rows, d_cols, nnz, N, col_tile, perm, rows_t, cols_t, stream));
+
+    Scratch tabs;  // tile_begin[ntile_c+2] | n_actv[ntile_c] | block_table[(ntile_c+1)*max_blk]
+    const size_t tb_n = (size_t)ntile_c + 2, bt_n = (size_t)((ntile_c + 1) * max_blk);
+    CK(tabs.reserve(sizeof(int32_t) * (tb_n + (size_t)ntile_c + bt_n)));
+    int32_t *tile_begin = (int32_t *)tabs.ptr, *n_actv = tile_begin + tb_n, *block_table = n_actv + ntile_c;
+    CK(cudaMemsetAsync(tabs.ptr, 0, tabs.bytes, stream));
+    Scratch act;
+    int32_t *active = nullptr;
+    if (out.active_row) {
+        CK(act.reserve(sizeof(int32_t) * (size_t)(M * ntile_c > 0 ? M * ntile_c : 1)));
+        CK(cudaMemsetAsync(act.ptr, 0, act.bytes, stream));
+        active = (int32_t *)act.ptr;
+    }
+
+    tile_begin_kernel<<<grid_for(ntile_c + 1), TPB, 0, stream>>>(cols_t, nnz, col_tile, (int)(ntile_c + 1), tile_begin);
+    CK(cudaGetLastError());
+    if (nnz > 0) {
+        seg_flag_kernel<<<grid_for(nnz), TPB, 0, stream>>>(rows_t, cols_t, nnz, col_tile, flag);
+        CK(cudaGetLastError());
+        size_t tmp_bytes = 0;
+        CK(cub::DeviceScan::InclusiveSum(nullptr, tmp_bytes, flag, segid, (int)nnz, stream));
+        Scratch tmp;
+        CK(tmp.reserve(tmp_bytes));
+        CK(cub::DeviceScan::InclusiveSum(tmp.ptr, tmp_bytes, flag, segid, (int)nnz, stream));
+        CK(cudaStreamSynchronize(stream));
+    }
+    block_table_prewrite_kernel<<<grid_for(n_loop), TPB, 0, stream>>>(tile_begin, (int)n_loop, max_blk, block_table);
+    CK(cudaGetLastError());
+    if (nnz > 0) {
+        tiling_tables_kernel<<<grid_for(nnz), TPB, 0, stream>>>(rows_t, cols_t, flag, segid, tile_begin, nnz, M,
+                                                               col_tile, panel_rows, max_blk, lrow,
+                                                               active, block_table, n_actv);
+        CK(cudaGetLastError());
+    }
+    // copy out.  lastIdx_tile[t] = tile_begin[t] for t <= n_loop; the slot past the
+    // loop (present when N is a multiple of col_tile) stays zero.
+    auto d2h = [&](void *dst, const void *src, size_t bytes) {
+        return dst ? cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream) : cudaSuccess;
+    };
+    if (nnz > 0) {
+        CK(d2h(out.tiled_ind, perm, sizeof(int32_t) * nnz));
+        CK(d2h(out.t_cols, cols_t, sizeof(int32_t) * nnz));
+    }
+    CK(cudaStreamSynchronize(stream));
+    if (out.lastIdx_tile) {
+        CK(cudaMemcpyAsync(out.lastIdx_tile, tile_begin, sizeof(int32_t) * (size_t)(n_loop + 1), cudaMemcpyDeviceToHost, stream));
+        for (int64_t t = n_loop + 1; t <= ntile_c; ++t) out.lastIdx_tile[t] = 0;
+    }
+    CK(d2h(out.lastIdx_block_tile, block_table, sizeof(int32_t) * bt_n));
+    CK(d2h(out.n_actv_row, n_actv, sizeof(int32_t) * (size_t)ntile_c));
+    if (active) CK(d2h(out.active_row, active, sizeof(int32_t) * (size_t)(M * ntile_c)));
+    if (nnz > 0) CK(d2h(out.t_rows, lrow, sizeof(int32_t) * nnz));
+    CK(cudaStreamSynchronize(stream));
+    if (out.max_active_row) {
+        int32_t mx = 0;
+        // small table: reduce on the host from the copied counts
+        int32_t *tmp_host = out.n_actv_row;
+        std::vector<int32_t> local;
+        if (!tmp_host) {
+            local.resize((size_t)ntile_c);
+            CK(cudaMemcpy(local.data(), n_actv, sizeof(int32_t) * (size_t)ntile_c, cudaMemcpyDeviceToHost));
+            tmp_host = local.data();
+        }
+        for (int64_t t = 0; t < ntile_c; ++t) mx = tmp_host[t] > mx ? tmp_host[t] : mx;
+        *out.max_active_row = mx;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace sddmm

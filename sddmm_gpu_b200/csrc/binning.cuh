@@ -1,0 +1,61 @@
+// GPU binning pass: everything the reference prepares on the host before its
+// launch loop (make_CSR, TiledMatrix, rewrite_matrix_1D -- HiPC18/src/util.h:52-65,
+// 131-153, 267-343), done on the device from the row-sorted COO.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace sddmm {
+
+// Device scratch whose lifetime is one binning call.
+struct Scratch {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    cudaError_t reserve(size_t n);
+    void release();
+    ~Scratch() { release(); }
+};
+
+// First offending nonzero index per class, or INT64_MAX when clean.
+struct ValidationResult {
+    long long first_unsorted;
+    long long first_out_of_range;
+};
+cudaError_t validate_coo(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M,
+                         int64_t N, ValidationResult *host_out, cudaStream_t stream);
+
+// row_ptr[r] = first nonzero of row r (M + 1 entries, empty rows repeat);
+// *d_nonempty receives the number of rows with at least one nonzero.
+cudaError_t build_row_ptr(const int32_t *d_rows, int64_t nnz, int64_t M, int64_t *d_row_ptr,
+                          unsigned long long *d_nonempty, cudaStream_t stream);
+
+// Number of distinct columns (marks a byte per column, then counts).
+cudaError_t count_distinct_cols(const int32_t *d_cols, int64_t nnz, int64_t N, int64_t *host_out,
+                                cudaStream_t stream);
+
+// Stable partition of the nonzeros by column tile (tile = col / col_tile):
+// d_perm[j] = input index of the j-th nonzero in tiled order (the reference's
+// tiled_ind, util.h:301), d_rows_t/d_cols_t the permuted indices.
+cudaError_t build_tiled_order(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t N,
+                              int col_tile, int32_t *d_perm, int32_t *d_rows_t, int32_t *d_cols_t,
+                              cudaStream_t stream);
+
+// Work items over the processing-order arrays: maximal runs of nonzeros that
+// share a column tile and a row panel (row / panel_rows), each cut into pieces of
+// at most item_nnz nonzeros.  Allocates *d_items (cudaMalloc) and sets *n_items.
+cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, int64_t nnz,
+                             int panel_rows, int col_tile, int item_nnz, WorkItem **d_items,
+                             int64_t *n_items, cudaStream_t stream);
+
+// Reference-layout tiling tables (test hook); see sddmm_plan_export_tiling.
+struct TilingTables {
+    int32_t *t_rows, *t_cols, *tiled_ind, *lastIdx_tile, *lastIdx_block_tile, *active_row, *n_actv_row;
+    int32_t *max_active_row;
+};
+cudaError_t export_reference_tiling(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M,
+                                    int64_t N, int panel_rows, int col_tile, const TilingTables &host_out,
+                                    cudaStream_t stream);
+
+}  // namespace sddmm

@@ -1,0 +1,58 @@
+// Shared declarations of the sm_100a SDDMM engine (internal; the public surface
+// is include/sddmm_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "sddmm_b200.h"
+
+namespace sddmm {
+
+// One unit of work of the row-panel kernel: a run of consecutive nonzeros (in the
+// plan's processing order) whose rows all lie in [row_begin, row_begin + n_rows),
+// n_rows <= the plan's panel height, so that the W rows they touch fit one
+// shared-memory panel.  Built on the device by the binning pass.
+struct WorkItem {
+    int64_t nnz_begin;
+    int32_t nnz_count;
+    int32_t row_begin;
+    int32_t n_rows;
+    int32_t reserved;
+};
+
+// Device status word written by kernels whose bounded waits give up.
+enum DeviceStatus : int { DEV_OK = 0, DEV_MBARRIER_TIMEOUT = 1 };
+
+struct PanelConfig {
+    int panel_rows;      // rows of W per staged panel
+    int item_nnz;        // nonzero budget of one work item
+    int threads;         // CTA size
+    int ctas_per_sm;     // resident CTAs per SM the launch is sized for
+    size_t smem_bytes;   // dynamic shared memory per CTA
+};
+
+// Chooses panel height / item budget / CTA shape for a given K and hint.
+PanelConfig choose_panel_config(int K, int panel_rows_hint, int sm_count, size_t smem_optin);
+
+// Planless kernel: every sub-warp group gathers its W row and H row from global
+// memory.  rows/cols/P in the same (input) order.
+cudaError_t launch_gather(const int32_t *rows, const int32_t *cols, const float *sval,
+                          const float *W, const float *H, float *P, int64_t nnz, int K,
+                          int sm_count, cudaStream_t stream);
+
+// Row-panel kernel: persistent CTAs walk the work items; the W rows an item
+// touches are staged into shared memory with bulk asynchronous copies (TMA,
+// double-buffered on mbarriers), H rows are gathered with 128-bit loads.
+// perm == nullptr: P[j] = result of processing-order nonzero j (sval indexed the
+// same way).  perm != nullptr: result of j goes to P[perm[j]], scaled by sval[perm[j]].
+cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *rows,
+                         const int32_t *cols, const int32_t *perm, const float *sval,
+                         const float *W, const float *H, float *P, int K,
+                         const PanelConfig &cfg, int sm_count, int *dev_status,
+                         cudaStream_t stream);
+
+// One-time per-process kernel attribute set-up (opt-in shared memory sizes).
+cudaError_t init_kernel_attributes(size_t smem_optin);
+
+}  // namespace sddmm

@@ -1,0 +1,506 @@
+// C ABI of the engine: handle, plan (GPU binning pass), execute.
+// Replaces the host driver sddmm_GPU of the reference (HiPC18/src/sddmm.cu:32-151):
+// device memory for the pattern is owned by a reusable plan instead of being
+// allocated and freed per call, errors come back as status codes instead of
+// assert(), and there is exactly one kernel launch per execute.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "binning.cuh"
+#include "common.cuh"
+#include "sddmm_b200.h"
+
+using namespace sddmm;
+
+struct sddmm_handle_s {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int *d_status = nullptr;  // device status word of bounded waits
+    int *h_status = nullptr;  // pinned mirror
+    std::string last_error;
+};
+
+struct sddmm_plan_s {
+    sddmm_handle_s *h = nullptr;
+    int64_t M = 0, N = 0, nnz = 0;
+    int K = 0;
+    int col_tile = 0;     // == N (clamped) when there is a single column tile
+    int n_col_tiles = 1;
+    PanelConfig cfg{};
+    // pattern, input order
+    int32_t *d_rows = nullptr, *d_cols = nullptr;
+    bool owns_indices = true;
+    // pattern, tiled order (only when n_col_tiles > 1)
+    int32_t *d_rows_t = nullptr, *d_cols_t = nullptr, *d_perm = nullptr;
+    int64_t *d_row_ptr = nullptr;
+    WorkItem *d_items = nullptr;
+    int64_t n_items = 0;
+    int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
+    // staging for host operands (allocated on first use)
+    float *d_W = nullptr, *d_H = nullptr, *d_S = nullptr, *d_P = nullptr;
+    int64_t device_bytes = 0;
+    float plan_ms = 0.f, last_ms = -1.f;
+};
+
+namespace {
+
+int fail_cuda(sddmm_handle_s *h, cudaError_t e, const char *what)
+{
+    if (h) {
+        h->last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    }
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return e == cudaErrorMemoryAllocation ? SDDMM_OUT_OF_MEMORY : SDDMM_CUDA_ERROR;
+}
+
+#define CUDA_TRY(h, expr)                                   \
+    do {                                                    \
+        cudaError_t _e = (expr);                            \
+        if (_e != cudaSuccess) return fail_cuda((h), _e, #expr); \
+    } while (0)
+
+bool is_device_ptr(const void *p)
+{
+    if (!p) return false;
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, p);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+int check_k(int K)
+{
+    if (K <= 0 || (K % 4) != 0 || K > SDDMM_MAX_K) return SDDMM_K_UNSUPPORTED;
+    return SDDMM_OK;
+}
+
+template <class T>
+cudaError_t dev_alloc(sddmm_plan_s *p, T **ptr, size_t count)
+{
+    size_t bytes = sizeof(T) * (count ? count : 1);
+    cudaError_t e = cudaMalloc((void **)ptr, bytes);
+    if (e == cudaSuccess) p->device_bytes += (int64_t)bytes;
+    return e;
+}
+
+void free_plan_memory(sddmm_plan_s *p)
+{
+    if (p->owns_indices) {
+        cudaFree(p->d_rows);
+        cudaFree(p->d_cols);
+    }
+    cudaFree(p->d_rows_t);
+    cudaFree(p->d_cols_t);
+    cudaFree(p->d_perm);
+    cudaFree(p->d_row_ptr);
+    cudaFree(p->d_items);
+    cudaFree(p->d_W);
+    cudaFree(p->d_H);
+    cudaFree(p->d_S);
+    cudaFree(p->d_P);
+}
+
+// After a synchronising point: turn the device status word into a status code.
+int check_device_status(sddmm_handle_s *h)
+{
+    if (*h->h_status != DEV_OK) {
+        h->last_error = "a bounded device-side wait (mbarrier) gave up";
+        *h->h_status = DEV_OK;
+        cudaMemsetAsync(h->d_status, 0, sizeof(int), h->stream);
+        return SDDMM_DEVICE_TIMEOUT;
+    }
+    return SDDMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *sddmm_status_string(int s)
+{
+    switch (s) {
+    case SDDMM_OK: return "ok";
+    case SDDMM_INVALID_ARG: return "invalid argument";
+    case SDDMM_UNSORTED_INPUT: return "input is not sorted by row";
+    case SDDMM_INDEX_OUT_OF_RANGE: return "row or column index out of range";
+    case SDDMM_K_UNSUPPORTED: return "K must be a positive multiple of 4 not larger than SDDMM_MAX_K";
+    case SDDMM_CUDA_ERROR: return "CUDA error";
+    case SDDMM_NCCL_ERROR: return "NCCL error";
+    case SDDMM_OUT_OF_MEMORY: return "out of device memory";
+    case SDDMM_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case SDDMM_IO_ERROR: return "I/O error";
+    case SDDMM_PARSE_ERROR: return "Matrix Market parse error";
+    case SDDMM_NO_DEVICE: return "no usable CUDA device (this engine has no CPU fallback)";
+    default: return "unknown status";
+    }
+}
+
+int sddmm_create(sddmm_handle_t *out, int device)
+{
+    if (!out) return SDDMM_INVALID_ARG;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return SDDMM_NO_DEVICE;
+    }
+    if (device < 0 || device >= n) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = new (std::nothrow) sddmm_handle_s;
+    if (!h) return SDDMM_OUT_OF_MEMORY;
+    h->device = device;
+    cudaError_t e = cudaSetDevice(device);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess && prop.major < 10) {
+        delete h;
+        return SDDMM_NO_DEVICE;  // kernels are built for sm_100a only
+    }
+    if (e == cudaSuccess) {
+        h->sm_count = prop.multiProcessorCount;
+        h->smem_optin = prop.sharedMemPerBlockOptin;
+        e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking);
+    }
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev1);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&h->d_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaHostAlloc((void **)&h->h_status, sizeof(int), cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        sddmm_destroy(h);
+        return SDDMM_CUDA_ERROR;
+    }
+    *h->h_status = DEV_OK;
+    h->stream = h->own_stream;
+    *out = h;
+    return SDDMM_OK;
+}
+
+int sddmm_destroy(sddmm_handle_t h)
+{
+    if (!h) return SDDMM_OK;
+    cudaSetDevice(h->device);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    if (h->ev0) cudaEventDestroy(h->ev0);
+    if (h->ev1) cudaEventDestroy(h->ev1);
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->h_status) cudaFreeHost(h->h_status);
+    (void)cudaGetLastError();
+    delete h;
+    return SDDMM_OK;
+}
+
+const char *sddmm_last_error(sddmm_handle_t h) { return h ? h->last_error.c_str() : ""; }
+
+int sddmm_set_stream(sddmm_handle_t h, void *cuda_stream)
+{
+    if (!h) return SDDMM_INVALID_ARG;
+    h->stream = cuda_stream ? (cudaStream_t)cuda_stream : h->own_stream;
+    return SDDMM_OK;
+}
+
+int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const int32_t *rows,
+                   const int32_t *cols, int K, int panel_rows_hint, int col_tile_hint, uint32_t flags,
+                   sddmm_plan_t *out)
+{
+    if (!h || !out) return SDDMM_INVALID_ARG;
+    *out = nullptr;
+    if (M < 0 || N < 0 || nnz < 0 || (nnz > 0 && (!rows || !cols))) return SDDMM_INVALID_ARG;
+    if (M > INT32_MAX || N > INT32_MAX || nnz >= INT32_MAX) return SDDMM_INVALID_ARG;  // int32 indices, as the reference
+    if (nnz > 0 && (M == 0 || N == 0)) return SDDMM_INDEX_OUT_OF_RANGE;
+    int st = check_k(K);
+    if (st != SDDMM_OK) return st;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+
+    sddmm_plan_s *p = new (std::nothrow) sddmm_plan_s;
+    if (!p) return SDDMM_OUT_OF_MEMORY;
+    p->h = h;
+    p->M = M; p->N = N; p->nnz = nnz; p->K = K;
+    cudaStream_t s = h->stream;
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+
+#define PLAN_TRY(expr)                                 \
+    do {                                               \
+        cudaError_t _e = (expr);                       \
+        if (_e != cudaSuccess) {                       \
+            int _st = fail_cuda(h, _e, #expr);         \
+            free_plan_memory(p);                       \
+            delete p;                                  \
+            if (t0) cudaEventDestroy(t0);              \
+            if (t1) cudaEventDestroy(t1);              \
+            return _st;                                \
+        }                                              \
+    } while (0)
+
+    const bool dev_idx = (flags & SDDMM_PLAN_DEVICE_INDICES) != 0;
+    if (dev_idx) {
+        p->d_rows = const_cast<int32_t *>(rows);
+        p->d_cols = const_cast<int32_t *>(cols);
+        p->owns_indices = false;
+    } else {
+        PLAN_TRY(dev_alloc(p, &p->d_rows, (size_t)nnz));
+        PLAN_TRY(dev_alloc(p, &p->d_cols, (size_t)nnz));
+        if (nnz > 0) {
+            PLAN_TRY(cudaMemcpyAsync(p->d_rows, rows, sizeof(int32_t) * nnz, cudaMemcpyHostToDevice, s));
+            PLAN_TRY(cudaMemcpyAsync(p->d_cols, cols, sizeof(int32_t) * nnz, cudaMemcpyHostToDevice, s));
+        }
+    }
+    PLAN_TRY(cudaEventCreate(&t0));
+    PLAN_TRY(cudaEventCreate(&t1));
+    PLAN_TRY(cudaEventRecord(t0, s));
+
+    if (!(flags & SDDMM_PLAN_SKIP_VALIDATION)) {
+        ValidationResult vr;
+        PLAN_TRY(validate_coo(p->d_rows, p->d_cols, nnz, M, N, &vr, s));
+        if (vr.first_out_of_range != LLONG_MAX || vr.first_unsorted != LLONG_MAX) {
+            char buf[160];
+            const bool oob = vr.first_out_of_range != LLONG_MAX;
+            snprintf(buf, sizeof(buf), "%s at nonzero %lld", oob ? "index out of range" : "rows not sorted",
+                     oob ? vr.first_out_of_range : vr.first_unsorted);
+            h->last_error = buf;
+            free_plan_memory(p);
+            delete p;
+            cudaEventDestroy(t0);
+            cudaEventDestroy(t1);
+            return oob ? SDDMM_INDEX_OUT_OF_RANGE : SDDMM_UNSORTED_INPUT;
+        }
+    }
+
+    // row pointer over all rows (empty rows included)
+    PLAN_TRY(dev_alloc(p, &p->d_row_ptr, (size_t)M + 1));
+    {
+        Scratch cnt;
+        PLAN_TRY(cnt.reserve(sizeof(unsigned long long)));
+        PLAN_TRY(build_row_ptr(p->d_rows, nnz, M, p->d_row_ptr, (unsigned long long *)cnt.ptr, s));
+        unsigned long long ne = 0;
+        PLAN_TRY(cudaMemcpyAsync(&ne, cnt.ptr, sizeof(ne), cudaMemcpyDeviceToHost, s));
+        PLAN_TRY(cudaStreamSynchronize(s));
+        p->n_nonempty_rows = (int64_t)ne;
+    }
+
+    // column tiles: a hint >= N (or <= 0) means one tile, the identity order
+    p->cfg = choose_panel_config(K, panel_rows_hint, h->sm_count, h->smem_optin);
+    int64_t ct = (col_tile_hint <= 0 || col_tile_hint >= N) ? (N > 0 ? N : 1) : col_tile_hint;
+    p->col_tile = (int)ct;
+    p->n_col_tiles = (int)((N + ct - 1) / ct);
+    if (p->n_col_tiles < 1) p->n_col_tiles = 1;
+    const int32_t *rows_p = p->d_rows, *cols_p = p->d_cols;
+    if (p->n_col_tiles > 1 && nnz > 0) {
+        PLAN_TRY(dev_alloc(p, &p->d_perm, (size_t)nnz));
+        PLAN_TRY(dev_alloc(p, &p->d_rows_t, (size_t)nnz));
+        PLAN_TRY(dev_alloc(p, &p->d_cols_t, (size_t)nnz));
+        PLAN_TRY(build_tiled_order(p->d_rows, p->d_cols, nnz, N, p->col_tile, p->d_perm, p->d_rows_t, p->d_cols_t, s));
+        rows_p = p->d_rows_t;
+        cols_p = p->d_cols_t;
+    }
+    PLAN_TRY(build_work_items(rows_p, cols_p, nnz, p->cfg.panel_rows, p->col_tile, p->cfg.item_nnz, &p->d_items,
+                              &p->n_items, s));
+    p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items);
+    PLAN_TRY(cudaEventRecord(t1, s));
+    PLAN_TRY(cudaEventSynchronize(t1));
+    PLAN_TRY(cudaEventElapsedTime(&p->plan_ms, t0, t1));
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+#undef PLAN_TRY
+    *out = p;
+    return SDDMM_OK;
+}
+
+int sddmm_destroy_plan(sddmm_plan_t p)
+{
+    if (!p) return SDDMM_OK;
+    cudaSetDevice(p->h->device);
+    cudaStreamSynchronize(p->h->stream);
+    free_plan_memory(p);
+    (void)cudaGetLastError();
+    delete p;
+    return SDDMM_OK;
+}
+
+int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *Sval, float *P, uint32_t flags)
+{
+    if (!p) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    if (p->nnz == 0) { p->last_ms = 0.f; return SDDMM_OK; }
+    if (!W || !H || !P) return SDDMM_INVALID_ARG;
+    const bool use_gather = (flags & SDDMM_FLAG_KERNEL_GATHER) != 0;
+    const bool tiled_out = (flags & SDDMM_FLAG_TILED_ORDER) != 0;
+    if (use_gather && (flags & SDDMM_FLAG_KERNEL_PANEL)) return SDDMM_INVALID_ARG;
+    if (use_gather && tiled_out && p->d_perm) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = h->stream;
+
+    const bool w_dev = is_device_ptr(W), h_dev = is_device_ptr(H), p_dev = is_device_ptr(P);
+    const bool s_dev = Sval ? is_device_ptr(Sval) : true;
+    const bool all_dev = w_dev && h_dev && p_dev && s_dev;
+    if ((flags & SDDMM_FLAG_ASYNC) && !all_dev) return SDDMM_INVALID_ARG;
+
+    const float *dW = W, *dH = H, *dS = Sval;
+    float *dP = P;
+    const size_t wbytes = sizeof(float) * (size_t)p->M * p->K, hbytes = sizeof(float) * (size_t)p->N * p->K;
+    const size_t nbytes = sizeof(float) * (size_t)p->nnz;
+    if (!h_dev) {
+        if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_H, H, hbytes, cudaMemcpyHostToDevice, s));
+        dH = p->d_H;
+    }
+    if (!w_dev) {
+        if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_W, W, wbytes, cudaMemcpyHostToDevice, s));
+        dW = p->d_W;
+    }
+    if (Sval && !s_dev) {
+        if (!p->d_S) CUDA_TRY(h, dev_alloc(p, &p->d_S, (size_t)p->nnz));
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_S, Sval, nbytes, cudaMemcpyHostToDevice, s));
+        dS = p->d_S;
+    }
+    if (!p_dev) {
+        if (!p->d_P) CUDA_TRY(h, dev_alloc(p, &p->d_P, (size_t)p->nnz));
+        dP = p->d_P;
+    }
+
+    CUDA_TRY(h, cudaEventRecord(h->ev0, s));
+    if (use_gather) {
+        CUDA_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
+    } else {
+        const bool tiled = p->d_perm != nullptr;
+        const int32_t *rows_p = tiled ? p->d_rows_t : p->d_rows;
+        const int32_t *cols_p = tiled ? p->d_cols_t : p->d_cols;
+        // tiled processing order: results go back to input order through the
+        // permutation unless the caller asked for the tiled order itself
+        const int32_t *perm = (tiled && !tiled_out) ? p->d_perm : nullptr;
+        if (tiled && tiled_out && dS) {
+            // S values are in input order; the tiled-order result is produced
+            // unscaled only (what the reference's kernel leaves in d_val)
+            h->last_error = "SDDMM_FLAG_TILED_ORDER with S values is not supported on a multi-tile plan";
+            return SDDMM_INVALID_ARG;
+        }
+        CUDA_TRY(h, launch_panel(p->d_items, p->n_items, rows_p, cols_p, perm, dS, dW, dH, dP, p->K, p->cfg,
+                                 h->sm_count, h->d_status, s));
+    }
+    CUDA_TRY(h, cudaEventRecord(h->ev1, s));
+    if (!p_dev) CUDA_TRY(h, cudaMemcpyAsync(P, dP, nbytes, cudaMemcpyDeviceToHost, s));
+    if (flags & SDDMM_FLAG_ASYNC) {
+        p->last_ms = -1.f;
+        return SDDMM_OK;
+    }
+    CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(h, cudaStreamSynchronize(s));
+    CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
+    return check_device_status(h);
+}
+
+int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms)
+{
+    if (!p || !ms) return SDDMM_INVALID_ARG;
+    *ms = p->last_ms;
+    return SDDMM_OK;
+}
+
+int sddmm_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const int32_t *rows, const int32_t *cols,
+              const float *Sval, const float *W, const float *H, int K, float *P)
+{
+    if (!h) return SDDMM_INVALID_ARG;
+    if (M < 0 || N < 0 || nnz < 0) return SDDMM_INVALID_ARG;
+    int st = check_k(K);
+    if (st != SDDMM_OK) return st;
+    if (nnz == 0) return SDDMM_OK;
+    if (!rows || !cols || !W || !H || !P) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = h->stream;
+    // Everything that is not already on the device is staged for this call only,
+    // as the reference does (sddmm.cu:38-73,147-150).
+    struct Tmp {
+        void *p[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+        ~Tmp() { for (void *q : p) if (q) cudaFree(q); }
+    } tmp;
+    auto stage = [&](int slot, const void *src, size_t bytes, const void **dst) -> cudaError_t {
+        if (is_device_ptr(src)) { *dst = src; return cudaSuccess; }
+        cudaError_t e = cudaMalloc(&tmp.p[slot], bytes);
+        if (e != cudaSuccess) return e;
+        *dst = tmp.p[slot];
+        return cudaMemcpyAsync(tmp.p[slot], src, bytes, cudaMemcpyHostToDevice, s);
+    };
+    const void *dr, *dc, *dw, *dh, *ds = nullptr;
+    CUDA_TRY(h, stage(0, rows, sizeof(int32_t) * nnz, &dr));
+    CUDA_TRY(h, stage(1, cols, sizeof(int32_t) * nnz, &dc));
+    CUDA_TRY(h, stage(2, W, sizeof(float) * (size_t)M * K, &dw));
+    CUDA_TRY(h, stage(3, H, sizeof(float) * (size_t)N * K, &dh));
+    if (Sval) CUDA_TRY(h, stage(4, Sval, sizeof(float) * nnz, &ds));
+    float *dp = P;
+    const bool p_dev = is_device_ptr(P);
+    if (!p_dev) {
+        CUDA_TRY(h, cudaMalloc(&tmp.p[5], sizeof(float) * nnz));
+        dp = (float *)tmp.p[5];
+    }
+    CUDA_TRY(h, launch_gather((const int32_t *)dr, (const int32_t *)dc, (const float *)ds, (const float *)dw,
+                              (const float *)dh, dp, nnz, K, h->sm_count, s));
+    if (!p_dev) CUDA_TRY(h, cudaMemcpyAsync(P, dp, sizeof(float) * nnz, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(h, cudaStreamSynchronize(s));
+    return SDDMM_OK;
+}
+
+int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info)
+{
+    if (!p || !info) return SDDMM_INVALID_ARG;
+    info->M = p->M; info->N = p->N; info->nnz = p->nnz; info->K = p->K;
+    info->panel_rows = p->cfg.panel_rows;
+    info->col_tile = p->col_tile;
+    info->n_col_tiles = p->n_col_tiles;
+    info->n_work_items = p->n_items;
+    info->n_nonempty_rows = p->n_nonempty_rows;
+    info->n_nonempty_cols = p->n_nonempty_cols;
+    info->device_bytes = p->device_bytes;
+    info->plan_ms = p->plan_ms;
+    return SDDMM_OK;
+}
+
+int sddmm_plan_count_cols(sddmm_plan_t p, int64_t *out)
+{
+    if (!p || !out) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    if (p->n_nonempty_cols < 0) {
+        CUDA_TRY(h, cudaSetDevice(h->device));
+        int64_t c = 0;
+        CUDA_TRY(h, count_distinct_cols(p->d_cols, p->nnz, p->N, &c, h->stream));
+        p->n_nonempty_cols = c;
+    }
+    *out = p->n_nonempty_cols;
+    return SDDMM_OK;
+}
+
+int sddmm_plan_export_row_ptr(sddmm_plan_t p, int64_t *row_ptr)
+{
+    if (!p || !row_ptr) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    CUDA_TRY(h, cudaMemcpyAsync(row_ptr, p->d_row_ptr, sizeof(int64_t) * (size_t)(p->M + 1), cudaMemcpyDeviceToHost,
+                                h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    return SDDMM_OK;
+}
+
+int sddmm_plan_export_tiling(sddmm_plan_t p, int panel_rows, int col_tile, int32_t *t_rows, int32_t *t_cols,
+                             int32_t *tiled_ind, int32_t *lastIdx_tile, int32_t *lastIdx_block_tile,
+                             int32_t *active_row, int32_t *n_actv_row, int32_t *max_active_row)
+{
+    if (!p || panel_rows <= 0 || col_tile <= 0) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    TilingTables t{t_rows, t_cols, tiled_ind, lastIdx_tile, lastIdx_block_tile, active_row, n_actv_row, max_active_row};
+    CUDA_TRY(h, export_reference_tiling(p->d_rows, p->d_cols, p->nnz, p->M, p->N, panel_rows, col_tile, t, h->stream));
+    return SDDMM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,159 @@
+// Drop-in command line of the reference program:
+//
+//     ./sddmm input.mtx K tile_size_X tile_size_Y [options]
+//
+// Same four positionals in the same order and with the meaning the reference's
+// code gives them (HiPC18/src/sddmm.cu:251-255): argv[3] is the row-panel height
+// (rows of W per shared-memory panel), argv[4] the column-tile width.  The same
+// three stdout lines are printed (sddmm.cu:267, :282, :114) so that scripts
+// scraping them keep working.  W and H are initialised as the reference does
+// (util.h:75-81).  Everything runs on the GPU through the C ABI; there is no CPU
+// path here.  Errors give a one-line message on stderr and a non-zero exit code
+// instead of assert().
+//
+// Options (after the positionals):
+//   --iters N          timed repetitions (default 1, as the reference); the
+//                      printed time is the mean kernel time per repetition
+//   --warmup N         untimed repetitions first (default 0)
+//   --no-scale-by-s    store the unscaled dot product, as the reference's GPU
+//                      and COO CPU paths do (default: P = S o (W H^T))
+//   --gather           use the planless gather kernel
+//   --device D         CUDA device (default 0)
+//   --dump-p FILE      write P (float32, input nonzero order) to FILE
+//   --json FILE        write a small JSON report (ms, GFLOP/s, plan sizes)
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "sddmm_b200.h"
+
+namespace {
+
+int die(const char *what, int status, const char *detail)
+{
+    std::fprintf(stderr, "sddmm: %s: %s%s%s\n", what, sddmm_status_string(status), (detail && *detail) ? " - " : "",
+                 detail ? detail : "");
+    return status ? status : 1;
+}
+
+void initial(std::vector<float> &X, long n, int k)
+{
+    srand48(0L);  // W and H restart the same stream, as in the reference
+    for (long i = 0; i < n * (long)k; ++i) X[(size_t)i] = (float)(0.1 * drand48());
+}
+
+}  // namespace
+
+int main(int argc, char **argv)
+{
+    if (argc < 5) {
+        std::fprintf(stderr, "usage: %s input.mtx K tile_size_X tile_size_Y [--iters N] [--warmup N] "
+                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE]\n", argv[0]);
+        return 2;
+    }
+    const char *path = argv[1];
+    const int K = std::atoi(argv[2]);
+    const int panel_rows = std::atoi(argv[3]);  // tile_sizeY / actv_row_size in the reference
+    const int col_tile = std::atoi(argv[4]);    // tile_sizeX in the reference
+    int iters = 1, warmup = 0, device = 0;
+    bool scale = true, gather = false;
+    const char *dump_p = nullptr, *json = nullptr;
+    for (int i = 5; i < argc; ++i) {
+        std::string a = argv[i];
+        auto need = [&](const char *name) -> const char * {
+            if (i + 1 >= argc) {
+                std::fprintf(stderr, "sddmm: %s needs a value\n", name);
+                std::exit(2);
+            }
+            return argv[++i];
+        };
+        if (a == "--iters") iters = std::atoi(need("--iters"));
+        else if (a == "--warmup") warmup = std::atoi(need("--warmup"));
+        else if (a == "--device") device = std::atoi(need("--device"));
+        else if (a == "--no-scale-by-s") scale = false;
+        else if (a == "--scale-by-s") scale = true;
+        else if (a == "--gather") gather = true;
+        else if (a == "--dump-p") dump_p = need("--dump-p");
+        else if (a == "--json") json = need("--json");
+        else {
+            std::fprintf(stderr, "sddmm: unknown option %s\n", a.c_str());
+            return 2;
+        }
+    }
+    if (iters < 1) iters = 1;
+
+    sddmm_mtx_t f = nullptr;
+    int64_t M = 0, N = 0, nnz = 0;
+    char err[256] = "";
+    int st = sddmm_mtx_open(path, &f, &M, &N, &nnz, err, sizeof(err));
+    if (st != SDDMM_OK) return die("reading input", st, err);
+    std::printf("\nMatrix info:  rows: %lld, cols: %lld, nnz: %lld\n", (long long)M, (long long)N, (long long)nnz);
+    std::vector<int32_t> rows((size_t)nnz), cols((size_t)nnz);
+    std::vector<float> vals((size_t)nnz);
+    st = sddmm_mtx_read(f, rows.data(), cols.data(), vals.data());
+    if (st != SDDMM_OK) return die("reading input", st, "");
+    std::printf("\nTilesize: X = %d, tilesize: Y = %d, TB: %d\n", col_tile, panel_rows, 256);
+    if (!sddmm_coo_is_row_sorted(nnz, rows.data()))
+        return die("input", SDDMM_UNSORTED_INPUT, "convert it with sddmm_coo_sort_rows first");
+
+    std::vector<float> W((size_t)M * K), H((size_t)N * K), P((size_t)nnz);
+    if (K > 0) {
+        initial(W, M, K);
+        initial(H, N, K);
+    }
+
+    sddmm_handle_t h = nullptr;
+    st = sddmm_create(&h, device);
+    if (st != SDDMM_OK) return die("creating the engine", st, "");
+    sddmm_plan_t plan = nullptr;
+    st = sddmm_plan_coo(h, M, N, nnz, rows.data(), cols.data(), K, panel_rows, col_tile, 0, &plan);
+    if (st != SDDMM_OK) {
+        int rc = die("planning", st, sddmm_last_error(h));
+        sddmm_destroy(h);
+        return rc;
+    }
+    const uint32_t flags = gather ? SDDMM_FLAG_KERNEL_GATHER : 0u;
+    const float *sval = scale ? vals.data() : nullptr;
+    double total_ms = 0;
+    for (int it = 0; it < warmup + iters; ++it) {
+        st = sddmm_execute(plan, W.data(), H.data(), sval, P.data(), flags);
+        if (st != SDDMM_OK) {
+            int rc = die("executing", st, sddmm_last_error(h));
+            sddmm_destroy_plan(plan);
+            sddmm_destroy(h);
+            return rc;
+        }
+        float ms = 0;
+        sddmm_last_kernel_ms(plan, &ms);
+        if (it >= warmup) total_ms += ms;
+    }
+    const double ms = total_ms / iters;
+    std::printf("\nTime for SDDMM with K = %d : %g ms\n", K, ms);
+
+    sddmm_plan_info info;
+    sddmm_plan_get_info(plan, &info);
+    if (dump_p) {
+        FILE *o = std::fopen(dump_p, "wb");
+        if (!o || std::fwrite(P.data(), sizeof(float), (size_t)nnz, o) != (size_t)nnz) return die("writing P", SDDMM_IO_ERROR, dump_p);
+        std::fclose(o);
+    }
+    if (json) {
+        FILE *o = std::fopen(json, "w");
+        if (!o) return die("writing report", SDDMM_IO_ERROR, json);
+        const double gflops = ms > 0 ? 2.0 * (double)nnz * K / (ms * 1e6) : 0.0;
+        std::fprintf(o,
+                     "{\"rows\": %lld, \"cols\": %lld, \"nnz\": %lld, \"K\": %d, \"kernel_ms\": %.6f, "
+                     "\"gflops\": %.3f, \"plan_ms\": %.4f, \"panel_rows\": %d, \"col_tile\": %d, "
+                     "\"n_col_tiles\": %d, \"work_items\": %lld, \"nonempty_rows\": %lld, \"scale_by_s\": %s, "
+                     "\"kernel\": \"%s\"}\n",
+                     (long long)M, (long long)N, (long long)nnz, K, ms, gflops, info.plan_ms, info.panel_rows,
+                     info.col_tile, info.n_col_tiles, (long long)info.n_work_items, (long long)info.n_nonempty_rows,
+                     scale ? "true" : "false", gather ? "gather" : "panel");
+        std::fclose(o);
+    }
+    sddmm_destroy_plan(plan);
+    sddmm_destroy(h);
+    return 0;
+}

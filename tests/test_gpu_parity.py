@@ -1,0 +1,227 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Oracle = oracle/sddmm_oracle.c (restatement of sddmm_CPU_COO / sddmm_CPU_CSR,
+HiPC18/src/sddmm.cu:153-200).  Tolerance: 1e-4 relative per nonzero for the
+values (fp32, reassociated sums); order and indices bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import assert_parity, random_coo
+from sddmm_gpu_b200 import api, synth
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = {"panel": api.FLAG_KERNEL_PANEL, "gather": api.FLAG_KERNEL_GATHER}
+
+
+def run_plan(engine, M, N, rows, cols, W, H, vals=None, flags=0, panel_rows=0, col_tile=0):
+    plan = engine.plan_coo(M, N, rows, cols, W.shape[1], panel_rows, col_tile)
+    P = np.full(rows.shape[0], np.nan, np.float32)
+    plan.execute(W, H, P, vals, flags)
+    info = plan.info()
+    plan.close()
+    return P, info
+
+
+def test_hand_computable(engine):
+    # 3 x 4, 5 nonzeros, K = 4, integer-valued operands -> exact results
+    rows = np.array([0, 0, 1, 2, 2], np.int32)
+    cols = np.array([0, 3, 1, 0, 2], np.int32)
+    vals = np.array([1, 2, 3, 4, 5], np.float32)
+    W = np.arange(12, dtype=np.float32).reshape(3, 4)
+    H = (np.arange(16, dtype=np.float32).reshape(4, 4) % 5) - 2
+    expect = np.array([(W[r] * H[c]).sum() for r, c in zip(rows, cols)], np.float32)
+    for flag in KERNELS.values():
+        P, _ = run_plan(engine, 3, 4, rows, cols, W, H, None, flag)
+        assert np.array_equal(P, expect)
+        P, _ = run_plan(engine, 3, 4, rows, cols, W, H, vals, flag)
+        assert np.array_equal(P, expect * vals)
+
+
+@pytest.mark.parametrize("kernel", list(KERNELS))
+@pytest.mark.parametrize("K", [4, 8, 12, 16, 20, 32, 36, 64, 100, 128, 192, 256, 260, 512, 1024, 2048])
+def test_every_k(engine, kernel, K):
+    rng = np.random.default_rng(K)
+    M, N = 257, 190
+    rows, cols = random_coo(rng, M, N, 6000, empty_rows=[0, 5, 6, 7, 100, 256])
+    vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+    W = rng.standard_normal((M, K)).astype(np.float32)
+    H = rng.standard_normal((N, K)).astype(np.float32)
+    P, _ = run_plan(engine, M, N, rows, cols, W, H, vals, KERNELS[kernel])
+    assert_parity(P, rows, cols, W, H, vals)
+    P, _ = run_plan(engine, M, N, rows, cols, W, H, None, KERNELS[kernel])
+    assert_parity(P, rows, cols, W, H, None)
+
+
+@pytest.mark.parametrize("kernel", list(KERNELS))
+def test_structure_edge_cases(engine, kernel):
+    rng = np.random.default_rng(7)
+    K = 32
+    flag = KERNELS[kernel]
+    cases = []
+    # nnz = 1, M = 1, N = 1, max column index, one row holding everything
+    cases.append((1, 1, np.array([0], np.int32), np.array([0], np.int32)))
+    cases.append((5, 9, np.array([4], np.int32), np.array([8], np.int32)))
+    cases.append((1, 300, np.zeros(300, np.int32), np.arange(300, dtype=np.int32)))
+    cases.append((300, 1, np.arange(300, dtype=np.int32), np.zeros(300, np.int32)))
+    r, c = random_coo(rng, 64, 5000, 3000, hub_row=17)          # one hub row with all N columns
+    cases.append((64, 5000, r, c))
+    r, c = random_coo(rng, 3000, 64, 9000, empty_rows=range(0, 1000))   # empty rows at the start
+    cases.append((3000, 64, r, c))
+    r, c = random_coo(rng, 3000, 64, 9000, empty_rows=range(2000, 3000))  # ... at the end
+    cases.append((3000, 64, r, c))
+    for M, N, rows, cols in cases:
+        W = rng.random((M, K), dtype=np.float32)
+        H = rng.random((N, K), dtype=np.float32)
+        P, info = run_plan(engine, M, N, rows, cols, W, H, None, flag)
+        assert_parity(P, rows, cols, W, H)
+        assert info.n_nonempty_rows == np.unique(rows).size
+
+
+def test_empty_matrix(engine):
+    plan = engine.plan_coo(10, 10, np.zeros(0, np.int32), np.zeros(0, np.int32), 8)
+    W = np.ones((10, 8), np.float32)
+    plan.execute(W, W, np.zeros(0, np.float32))
+    assert plan.info().n_work_items == 0
+    assert np.array_equal(plan.export_row_ptr(), np.zeros(11, np.int64))
+    plan.close()
+
+
+def test_row_ptr_and_counts(engine):
+    rng = np.random.default_rng(3)
+    M, N = 1000, 777
+    rows, cols = random_coo(rng, M, N, 5000, empty_rows=[0, 1, 2, 500, 999])
+    plan = engine.plan_coo(M, N, rows, cols, 16)
+    rp = plan.export_row_ptr()
+    expect = np.zeros(M + 1, np.int64)
+    np.add.at(expect, rows.astype(np.int64) + 1, 1)
+    assert np.array_equal(rp, np.cumsum(expect))
+    assert plan.count_cols() == np.unique(cols).size
+    plan.close()
+
+
+def test_validation_errors(engine):
+    W = np.zeros((4, 8), np.float32)
+    rows = np.array([0, 2, 1], np.int32)
+    cols = np.array([0, 1, 2], np.int32)
+    with pytest.raises(api.SddmmError) as e:
+        engine.plan_coo(4, 4, rows, cols, 8)
+    assert e.value.status == api.UNSORTED_INPUT
+    with pytest.raises(api.SddmmError) as e:
+        engine.plan_coo(4, 4, np.array([0, 1, 4], np.int32), cols, 8)
+    assert e.value.status == api.INDEX_OUT_OF_RANGE
+    with pytest.raises(api.SddmmError) as e:
+        engine.plan_coo(4, 4, np.array([0, 1, 2], np.int32), np.array([0, -1, 2], np.int32), 8)
+    assert e.value.status == api.INDEX_OUT_OF_RANGE
+    for K in (0, 3, 30, 4100):
+        with pytest.raises(api.SddmmError) as e:
+            engine.plan_coo(4, 4, np.array([0, 1, 2], np.int32), cols, K)
+        assert e.value.status == api.K_UNSUPPORTED
+    # the handle stays usable after an error
+    plan = engine.plan_coo(4, 4, np.array([0, 1, 2], np.int32), cols, 8)
+    P = np.zeros(3, np.float32)
+    plan.execute(W, W, P)
+    plan.close()
+
+
+@pytest.mark.parametrize("col_tile,panel_rows", [(64, 16), (33, 7), (1, 1), (500, 192), (128, 0)])
+def test_column_tiled_plan(engine, col_tile, panel_rows):
+    # a multi-tile plan processes in the reference's tiled order and still
+    # returns P in input order; TILED_ORDER returns what sddmm_GPU leaves in d_val
+    rng = np.random.default_rng(11)
+    M, N, K = 300, 200, 64
+    rows, cols = random_coo(rng, M, N, 5003)
+    vals = rng.integers(1, 20, rows.shape[0]).astype(np.float32)
+    W = rng.random((M, K), dtype=np.float32)
+    H = rng.random((N, K), dtype=np.float32)
+    P, info = run_plan(engine, M, N, rows, cols, W, H, vals, 0, panel_rows, col_tile)
+    assert info.n_col_tiles == -(-N // col_tile)
+    ref = assert_parity(P, rows, cols, W, H, vals)
+    Pt, _ = run_plan(engine, M, N, rows, cols, W, H, None, api.FLAG_TILED_ORDER, panel_rows, col_tile)
+    tiling = oracle.cpu.rewrite_matrix_1d(rows, cols, vals, M, N, max(panel_rows, 1), col_tile)
+    P_unscaled, _ = run_plan(engine, M, N, rows, cols, W, H, None, 0, panel_rows, col_tile)
+    assert np.array_equal(Pt, P_unscaled[tiling["tiled_ind"]])
+    del ref
+
+
+def test_device_pointers_and_stream(engine):
+    p = synth.uniform_sparse(M=2048, N=1024, density=0.004, K=64, device="cuda")
+    rows, cols, W, H, vals = p["rows"], p["cols"], p["W"], p["H"], p["vals"] * 3
+    engine.set_stream(torch.cuda.current_stream().cuda_stream)
+    plan = engine.plan_coo(p["M"], p["N"], rows, cols, p["K"])
+    P = torch.empty(rows.shape[0], device="cuda")
+    plan.execute(W, H, P, vals, api.FLAG_ASYNC)
+    torch.cuda.synchronize()
+    engine.set_stream(None)
+    q = synth.to_numpy(p)
+    assert_parity(P.cpu().numpy(), q["rows"], q["cols"], q["W"], q["H"], q["vals"] * 3)
+    # one-shot form, host pointers
+    P2 = np.zeros(rows.shape[0], np.float32)
+    engine.sddmm_coo(p["M"], p["N"], q["rows"], q["cols"], q["W"], q["H"], p["K"], P2)
+    assert_parity(P2, q["rows"], q["cols"], q["W"], q["H"])
+    plan.close()
+
+
+def _scaled(problem_fn, **kw):
+    return synth.to_numpy(problem_fn(device="cpu", **kw))
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3_small", "c4_small", "c5_small"])
+@pytest.mark.parametrize("kernel", list(KERNELS))
+def test_benchmark_configs(engine, name, kernel):
+    # config 1 and 2 at full size; 3, 4, 5 at sizes the oracle finishes in seconds
+    if name == "c1":
+        p = _scaled(synth.uniform_sparse)
+    elif name == "c2":
+        p = _scaled(synth.bag_of_words)
+    elif name == "c3_small":
+        p = _scaled(synth.rmat, scale=14, edge_factor=16, K=128)
+    elif name == "c4_small":
+        p = _scaled(synth.rmat, scale=15, edge_factor=24, K=256, seed=synth.SEEDS["c4"])
+    else:
+        p = _scaled(synth.attention_mask, M=4096, half_width=64, n_global=12, K=64)
+    P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], KERNELS[kernel],
+                       p["panel_rows"], p["col_tile"])
+    assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+    assert info.nnz == p["rows"].shape[0]
+
+
+def test_repeatable_and_reusable_plan(engine):
+    # same plan, different operands; identical calls give identical bits
+    rng = np.random.default_rng(5)
+    M, N, K = 500, 400, 128
+    rows, cols = random_coo(rng, M, N, 20000)
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    outs = []
+    for seed in (1, 2, 1):
+        r = np.random.default_rng(seed)
+        W = r.standard_normal((M, K)).astype(np.float32)
+        H = r.standard_normal((N, K)).astype(np.float32)
+        P = np.zeros(rows.shape[0], np.float32)
+        plan.execute(W, H, P)
+        assert_parity(P, rows, cols, W, H)
+        outs.append(P)
+    assert np.array_equal(outs[0], outs[2])
+    plan.close()
+
+
+def test_linearity_at_scale(engine):
+    # size-independent property on a larger input: SDDMM is linear in W
+    p = synth.rmat(scale=18, edge_factor=16, K=128, device="cuda")
+    plan = engine.plan_coo(p["M"], p["N"], p["rows"], p["cols"], p["K"])
+    nnz = p["rows"].shape[0]
+    P1, P2, P3 = (torch.empty(nnz, device="cuda") for _ in range(3))
+    W2 = torch.randn_like(p["W"])
+    plan.execute(p["W"], p["H"], P1)
+    plan.execute(W2, p["H"], P2)
+    plan.execute(p["W"] + W2, p["H"], P3)
+    scale = (p["W"].abs().max() + W2.abs().max()) * p["H"].abs().max() * p["K"]
+    assert float((P1 + P2 - P3).abs().max()) <= 1e-5 * float(scale)
+    # and both kernels agree with each other to rounding
+    P4 = torch.empty(nnz, device="cuda")
+    plan.execute(p["W"], p["H"], P4, None, api.FLAG_KERNEL_GATHER)
+    assert float((P1 - P4).abs().max()) <= 1e-5 * float(scale)
+    plan.close()

@@ -1,0 +1,99 @@
+"""The CPU oracle against the golden fixtures (outputs of the reference's own
+functions, see tests/golden/make_golden.py) and, when the reference-built
+checker library is present, against the reference directly on fresh inputs."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "sddmm_*.npz"))))
+def test_sddmm_values_bit_exact(path):
+    g = np.load(path)
+    P = oracle.cpu.sddmm_coo(g["rows"], g["cols"], g["W"], g["H"])
+    assert np.array_equal(P, g["P_coo"])                      # sddmm_CPU_COO: unscaled
+    P = oracle.cpu.sddmm_csr(g["row_ptr"], g["cols"], g["vals"], g["W"], g["H"])
+    assert np.array_equal(P, g["P_csr"])                      # sddmm_CPU_CSR: scaled by S
+    P = oracle.cpu.sddmm_coo(g["rows"], g["cols"], g["W"], g["H"], g["vals"])
+    assert np.array_equal(P, g["P_csr"])
+    for threads in (1, 3):
+        assert np.array_equal(oracle.cpu.sddmm_coo(g["rows"], g["cols"], g["W"], g["H"], threads=threads), g["P_coo"])
+    # the float64 arbiter agrees with the fp32 loop to fp32 rounding
+    P64, A = oracle.cpu.sddmm_coo_f64(g["rows"], g["cols"], g["W"], g["H"])
+    assert np.all(np.abs(P64 - g["P_coo"]) <= 1e-5 * A + 1e-30)
+
+
+def test_tiling_tables_bit_exact():
+    g = np.load(os.path.join(GOLD, "tiling.npz"))
+    M, N = int(g["M"]), int(g["N"])
+    for i, (pr, ct) in enumerate(g["pairs"]):
+        t = oracle.cpu.rewrite_matrix_1d(g["rows"], g["cols"], g["vals"], M, N, int(pr), int(ct))
+        for k, v in t.items():
+            assert np.array_equal(np.asarray(v), g[f"t{i}_{k}"]), (pr, ct, k)
+    rp, rh, n_holder = oracle.cpu.make_csr(g["rows"], M)
+    assert np.array_equal(rp[: n_holder + 2], g["csr_row_ptr"][: n_holder + 2])
+    assert np.array_equal(rh[:n_holder], g["csr_row_holder"][:n_holder])
+
+
+def test_initial_bit_exact():
+    g = np.load(os.path.join(GOLD, "initial.npz"))
+    assert np.array_equal(oracle.cpu.initial(40, 12), g["X"])
+    # W and H restart the same stream (util.h:76): a shorter matrix is a prefix
+    assert np.array_equal(oracle.cpu.initial(10, 12), g["X"][:10])
+
+
+def test_conversion_bit_exact():
+    g = np.load(os.path.join(GOLD, "convert.npz"))
+    r, c, v, rp, n = oracle.cpu.unsorted_make_csr(g["rows_in"], g["cols_in"], g["vals_in"], int(g["M"]), int(g["N"]))
+    assert n == g["rows_in"].shape[0]
+    assert np.array_equal(r, g["rows_out"]) and np.array_equal(c, g["cols_out"])
+    assert np.array_equal(v, g["vals_out"]) and np.array_equal(rp, g["row_ptr"])
+    # the dump starts with "n_cols n_rows nnz" and 1-based triples of the transpose
+    assert g["dump_head"][0].split() == [str(int(g["N"])), str(int(g["M"])), str(n)]
+    assert g["dump_head"][1].split()[:2] == [str(r[0]), str(c[0])]
+
+
+@pytest.mark.skipif(oracle.ref is None, reason="reference-built checker not present")
+def test_oracle_against_reference_on_fresh_inputs():
+    rng = np.random.default_rng(99)
+    for M, N, K, nnz in [(33, 47, 4, 301), (200, 64, 36, 2999), (17, 300, 128, 1501)]:
+        cells = np.sort(rng.choice(M * N, nnz, replace=False))
+        rows, cols = (cells // N).astype(np.int32), (cells % N).astype(np.int32)
+        vals = rng.standard_normal(nnz).astype(np.float32)
+        W = rng.standard_normal((M, K)).astype(np.float32)
+        H = rng.standard_normal((N, K)).astype(np.float32)
+        assert np.array_equal(oracle.cpu.sddmm_coo(rows, cols, W, H), oracle.ref.sddmm_cpu_coo(rows, cols, vals, M, N, W, H))
+        rp = np.zeros(M + 1, np.int64)
+        np.add.at(rp, rows.astype(np.int64) + 1, 1)
+        rp = np.cumsum(rp)
+        assert np.array_equal(oracle.cpu.sddmm_csr(rp, cols, vals, W, H),
+                              oracle.ref.sddmm_cpu_csr(rp.astype(np.int32), cols, vals, M, N, W, H))
+        for pr, ct in [(5, 16), (192, 50000), (3, 1000)]:
+            a = oracle.cpu.rewrite_matrix_1d(rows, cols, vals, M, N, pr, ct)
+            b = oracle.ref.rewrite_matrix_1d(rows, cols, vals, M, N, pr, ct)
+            for k in a:
+                assert np.array_equal(np.asarray(a[k]), np.asarray(b[k])), (M, N, pr, ct, k)
+
+
+def test_empty_rows_are_defined():
+    # the reference reads uninitialised slots when rows are empty; the oracle
+    # defines the behaviour: empty rows are skipped
+    rows = np.array([2, 2, 5, 9], np.int32)
+    cols = np.array([0, 3, 1, 2], np.int32)
+    rp, rh, n = oracle.cpu.make_csr(rows, 12)
+    assert n == 3 and list(rh[:3]) == [2, 5, 9] and list(rp[:4]) == [0, 2, 3, 4]
+    t = oracle.cpu.rewrite_matrix_1d(rows, cols, None, 12, 4, 2, 2)
+    assert list(t["tiled_ind"]) == [0, 2, 1, 3]
+    assert list(t["rows"]) == [0, 1, 0, 1]
+    assert list(t["n_actv_row"][:2]) == [2, 2]
+
+
+def test_make_csc_cuts():
+    cols = np.array([0, 0, 1, 2, 2, 2, 3, 5, 5, 7], np.int32)
+    cir, nir = oracle.cpu.make_csc_cuts(cols, 8, 2)
+    assert nir.sum() == cols.size and len(cir) >= 2
