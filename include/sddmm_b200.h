@@ -75,8 +75,9 @@ SDDMM_API const char *sddmm_last_error(sddmm_handle_t h);
 
 /*
  * Run on a caller-owned CUDA stream (a cudaStream_t passed as void*) instead of
- * the handle's own; NULL restores the handle's stream.  The reference launches
- * on its private stream[0] (sddmm.cu:81-84,102).
+ * the handle's own; NULL restores the handle's stream (to launch on the legacy
+ * default stream pass cudaStreamLegacy, not 0).  The reference launches on its
+ * private stream[0] (sddmm.cu:81-84,102).
  */
 SDDMM_API int sddmm_set_stream(sddmm_handle_t h, void *cuda_stream);
 

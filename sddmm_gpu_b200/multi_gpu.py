@@ -1,0 +1,100 @@
+"""Row-block sharding of one SDDMM across the GPUs of a box, one process per GPU.
+
+Replaces the MPI variant of the reference (HiPC18_mpi/sddmm.cu:139-351,
+HiPC18_mpi/util.h:100-135): there every rank parses the whole file, redoes the
+whole preprocessing, uploads all of W and H and processes one nnz-balanced
+COLUMN panel, with MPI used for barriers only.  Here S is cut into nnz-balanced
+blocks of consecutive ROWS (so each rank's nonzeros are one contiguous slice of
+the input and the concatenation of the ranks' outputs is P in input order), rank
+r keeps only its rows of W, and H -- the one operand every rank needs whole -- is
+broadcast once per H version over NCCL (NVLink / NVSwitch).  P stays sharded.
+
+The collective is ``torch.distributed`` plumbing; the compute on each rank is the
+same C-ABI plan/execute as on one GPU.  Nothing here computes on the CPU.
+"""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import api
+
+
+class RowShard:
+    """What one rank owns: rows [row_begin, row_end), nonzeros [nnz_begin, nnz_end)."""
+
+    def __init__(self, rank, world, cuts, nnz_cuts):
+        self.rank, self.world = rank, world
+        self.cuts, self.nnz_cuts = cuts, nnz_cuts
+        self.row_begin, self.row_end = int(cuts[rank]), int(cuts[rank + 1])
+        self.nnz_begin, self.nnz_end = int(nnz_cuts[rank]), int(nnz_cuts[rank + 1])
+
+    @property
+    def n_rows(self):
+        return self.row_end - self.row_begin
+
+    @property
+    def nnz(self):
+        return self.nnz_end - self.nnz_begin
+
+
+def make_shard(M, rows_host, world, rank, align_rows=32):
+    """nnz-balanced row cuts (sddmm_partition_rows) -> this rank's shard.
+    rows_host: the row index of every nonzero (row-sorted), numpy int32."""
+    cuts, nnz_cuts = api.partition_rows(M, rows_host, world, align_rows)
+    return RowShard(rank, world, cuts, nnz_cuts)
+
+
+def local_pattern(shard, rows, cols):
+    """This rank's slice of the pattern with rows rebased to the shard (tensors or arrays)."""
+    a, b = shard.nnz_begin, shard.nnz_end
+    return rows[a:b] - shard.row_begin, cols[a:b]
+
+
+def broadcast_h(H, src=0, group=None, chunks=1):
+    """Broadcast H from `src` into every rank's own memory (in place).  With
+    chunks > 1 the rows of H go out as that many separate collectives, so that
+    work depending only on the early ones can be enqueued behind them."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return []
+    handles = []
+    n = H.shape[0]
+    step = -(-n // chunks)
+    for c0 in range(0, n, step):
+        handles.append(dist.broadcast(H[c0:c0 + step], src=src, group=group, async_op=True))
+    return handles
+
+
+def gather_p(P_local, shard, group=None):
+    """All ranks' P slices concatenated in input order (optional; P normally stays sharded)."""
+    if not dist.is_initialized() or shard.world == 1:
+        return P_local
+    sizes = [int(shard.nnz_cuts[g + 1] - shard.nnz_cuts[g]) for g in range(shard.world)]
+    out = [torch.empty(s, dtype=P_local.dtype, device=P_local.device) for s in sizes]
+    dist.all_gather(out, P_local, group=group)
+    return torch.cat(out)
+
+
+class ShardedSddmm:
+    """One rank's plan over its row block.  execute() takes this rank's W rows,
+    the full (already broadcast) H and returns this rank's slice of P."""
+
+    def __init__(self, handle, M, N, rows, cols, K, rows_host=None, world=None, rank=None, panel_rows_hint=0,
+                 col_tile_hint=0, align_rows=32):
+        world = world if world is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+        rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
+        if rows_host is None:
+            rows_host = rows.cpu().numpy() if hasattr(rows, "cpu") else np.asarray(rows)
+        self.shard = make_shard(M, rows_host, world, rank, align_rows)
+        lr, lc = local_pattern(self.shard, rows, cols)
+        if hasattr(lr, "contiguous"):
+            lr, lc = lr.contiguous(), lc.contiguous()
+        else:
+            lr, lc = np.ascontiguousarray(lr), np.ascontiguousarray(lc)
+        self.plan = handle.plan_coo(self.shard.n_rows, N, lr, lc, K, panel_rows_hint, col_tile_hint)
+        self.K = K
+
+    def execute(self, W_local, H, P_local, Sval_local=None, flags=0):
+        self.plan.execute(W_local, H, P_local, Sval_local, flags)
+
+    def close(self):
+        self.plan.close()

@@ -150,11 +150,18 @@ def test_column_tiled_plan(engine, col_tile, panel_rows):
 def test_device_pointers_and_stream(engine):
     p = synth.uniform_sparse(M=2048, N=1024, density=0.004, K=64, device="cuda")
     rows, cols, W, H, vals = p["rows"], p["cols"], p["W"], p["H"], p["vals"] * 3
-    engine.set_stream(torch.cuda.current_stream().cuda_stream)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    engine.set_stream(side.cuda_stream)
     plan = engine.plan_coo(p["M"], p["N"], rows, cols, p["K"])
     P = torch.empty(rows.shape[0], device="cuda")
-    plan.execute(W, H, P, vals, api.FLAG_ASYNC)
-    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        plan.execute(W, H, P, vals, api.FLAG_ASYNC)
+        e1.record()
+    side.synchronize()                  # only the caller's stream is waited for
+    assert e0.elapsed_time(e1) > 0.0
     engine.set_stream(None)
     q = synth.to_numpy(p)
     assert_parity(P.cpu().numpy(), q["rows"], q["cols"], q["W"], q["H"], q["vals"] * 3)
