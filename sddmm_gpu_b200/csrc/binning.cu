@@ -146,10 +146,54 @@ __global__ void fill_items_kernel(const int32_t *__restrict__ run_start, const i
         w.nnz_begin = b;
         w.nnz_count = (int32_t)(e - b);
         w.row_begin = rows[b];
-        w.n_rows = rows[e - 1] - w.row_begin + 1;
+        w.n_rows = 0;      // filled by count_item_rows_kernel
+        w.list_begin = 0;  // filled by set_list_begin_kernel
         w.reserved = 0;
         items[t] = w;
     }
+}
+
+// A nonzero heads a (work item, row) group when it opens an item or its row
+// differs from its predecessor's.
+struct ItemRowHead {
+    const int32_t *rows;
+    const unsigned char *item_start;
+    __device__ __forceinline__ bool operator()(int j) const
+    {
+        return item_start[j] || rows[j] != rows[j - 1];  // item_start[0] is always set
+    }
+};
+
+__global__ void mark_item_starts_kernel(const WorkItem *__restrict__ items, int64_t n_items, unsigned char *flag)
+{
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_items; t += (int64_t)gridDim.x * blockDim.x)
+        flag[items[t].nnz_begin] = 1;
+}
+
+// One warp per item: number of distinct rows among its nonzeros.
+__global__ void count_item_rows_kernel(WorkItem *items, int64_t n_items, const int32_t *__restrict__ rows,
+                                       int64_t *n_rows_out)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t t = warp; t < n_items; t += n_warps) {
+        const int64_t b = items[t].nnz_begin;
+        const int n = items[t].nnz_count;
+        int heads = 0;
+        for (int o = lane; o < n; o += 32) heads += (o == 0 || rows[b + o] != rows[b + o - 1]) ? 1 : 0;
+        for (int s = 16; s; s >>= 1) heads += __shfl_xor_sync(0xffffffffu, heads, s);
+        if (lane == 0) {
+            items[t].n_rows = heads;
+            n_rows_out[t] = heads;
+        }
+    }
+}
+
+__global__ void set_list_begin_kernel(WorkItem *items, int64_t n_items, const int64_t *__restrict__ list_off)
+{
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_items; t += (int64_t)gridDim.x * blockDim.x)
+        items[t].list_begin = list_off[t];
 }
 
 #define CK(x)                         \
@@ -229,10 +273,12 @@ cudaError_t build_tiled_order(const int32_t *d_rows, const int32_t *d_cols, int6
 
 cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, int64_t nnz, int panel_rows,
                              int col_tile, int item_nnz, WorkItem **d_items, int64_t *n_items,
-                             cudaStream_t stream)
+                             int32_t **d_item_rows, int64_t *n_item_rows, cudaStream_t stream)
 {
     *d_items = nullptr;
     *n_items = 0;
+    *d_item_rows = nullptr;
+    *n_item_rows = 0;
     if (nnz == 0) return cudaSuccess;
     const int n = (int)nnz;
     RunHead head{d_rows_p, d_cols_p, panel_rows, col_tile};
@@ -282,13 +328,47 @@ cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, i
     CK(cudaMalloc(&items, sizeof(WorkItem) * (size_t)total));
     fill_items_kernel<<<grid_for(total), TPB, 0, stream>>>(run_start, item_off, n_runs, total, d_rows_p, items);
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+
+    // 5. the distinct rows of every item, concatenated in item order
+    int32_t *item_rows = nullptr;
+    int64_t n_list = 0;
+    auto body = [&]() -> cudaError_t {
+        Scratch per_item;  // n_rows int64[total+1] | list_off int64[total+1]
+        CK(per_item.reserve(sizeof(int64_t) * 2 * ((size_t)total + 1)));
+        int64_t *cnt = (int64_t *)per_item.ptr, *list_off = cnt + (total + 1);
+        CK(cudaMemsetAsync(cnt + total, 0, sizeof(int64_t), stream));
+        Scratch flags;
+        CK(flags.reserve((size_t)nnz));
+        CK(cudaMemsetAsync(flags.ptr, 0, (size_t)nnz, stream));
+        mark_item_starts_kernel<<<grid_for(total), TPB, 0, stream>>>(items, total, (unsigned char *)flags.ptr);
+        count_item_rows_kernel<<<grid_for(total * 32), TPB, 0, stream>>>(items, total, d_rows_p, cnt);
+        CK(cudaGetLastError());
+        size_t tb = 0;
+        CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, cnt, list_off, (int)(total + 1), stream));
+        CK(tmp.reserve(tb));
+        CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, cnt, list_off, (int)(total + 1), stream));
+        set_list_begin_kernel<<<grid_for(total), TPB, 0, stream>>>(items, total, list_off);
+        CK(cudaGetLastError());
+        CK(cudaMemcpyAsync(&n_list, list_off + total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+        CK(cudaStreamSynchronize(stream));
+        CK(cudaMalloc(&item_rows, sizeof(int32_t) * (size_t)(n_list > 0 ? n_list : 1)));
+        auto head_flags = thrust::make_transform_iterator(counting, ItemRowHead{d_rows_p, (const unsigned char *)flags.ptr});
+        tb = 0;
+        CK(cub::DeviceSelect::Flagged(nullptr, tb, d_rows_p, head_flags, item_rows, d_n_sel, n, stream));
+        CK(tmp.reserve(tb));
+        CK(cub::DeviceSelect::Flagged(tmp.ptr, tb, d_rows_p, head_flags, item_rows, d_n_sel, n, stream));
+        return cudaStreamSynchronize(stream);
+    };
+    if (e == cudaSuccess) e = body();
     if (e != cudaSuccess) {
         cudaFree(items);
+        if (item_rows) cudaFree(item_rows);
         return e;
     }
     *d_items = items;
     *n_items = total;
+    *d_item_rows = item_rows;
+    *n_item_rows = n_list;
     return cudaSuccess;
 }
 

@@ -44,10 +44,13 @@ cudaError_t build_tiled_order(const int32_t *d_rows, const int32_t *d_cols, int6
 
 // Work items over the processing-order arrays: maximal runs of nonzeros that
 // share a column tile and a row panel (row / panel_rows), each cut into pieces of
-// at most item_nnz nonzeros.  Allocates *d_items (cudaMalloc) and sets *n_items.
+// at most item_nnz nonzeros, plus the list of the distinct rows of every item
+// (what the producer warp stages).  Allocates *d_items and *d_item_rows
+// (cudaMalloc) and sets *n_items / *n_item_rows.
 cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, int64_t nnz,
                              int panel_rows, int col_tile, int item_nnz, WorkItem **d_items,
-                             int64_t *n_items, cudaStream_t stream);
+                             int64_t *n_items, int32_t **d_item_rows, int64_t *n_item_rows,
+                             cudaStream_t stream);
 
 // Reference-layout tiling tables (test hook); see sddmm_plan_export_tiling.
 struct TilingTables {

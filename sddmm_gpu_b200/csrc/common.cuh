@@ -14,10 +14,11 @@ namespace sddmm {
 // n_rows <= the plan's panel height, so that the W rows they touch fit one
 // shared-memory panel.  Built on the device by the binning pass.
 struct WorkItem {
-    int64_t nnz_begin;
+    int64_t nnz_begin;   // first nonzero (processing order)
+    int64_t list_begin;  // offset of the item's distinct rows in the plan's item-row list
     int32_t nnz_count;
-    int32_t row_begin;
-    int32_t n_rows;
+    int32_t row_begin;   // smallest row of the item
+    int32_t n_rows;      // number of distinct rows (entries of the item-row list)
     int32_t reserved;
 };
 
@@ -42,12 +43,13 @@ cudaError_t launch_gather(const int32_t *rows, const int32_t *cols, const float 
                           int sm_count, cudaStream_t stream);
 
 // Row-panel kernel: persistent CTAs walk the work items; the W rows an item
-// touches are staged into shared memory with bulk asynchronous copies (TMA,
-// double-buffered on mbarriers), H rows are gathered with 128-bit loads.
+// touches (item_rows lists them) are staged into shared memory with bulk
+// asynchronous copies (TMA, double-buffered on mbarriers) by a producer warp,
+// H rows are gathered with software-pipelined 128-bit loads.
 // perm == nullptr: P[j] = result of processing-order nonzero j (sval indexed the
 // same way).  perm != nullptr: result of j goes to P[perm[j]], scaled by sval[perm[j]].
-cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *rows,
-                         const int32_t *cols, const int32_t *perm, const float *sval,
+cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *item_rows,
+                         const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                          const float *W, const float *H, float *P, int K,
                          const PanelConfig &cfg, int sm_count, int *dev_status,
                          cudaStream_t stream);

@@ -43,6 +43,8 @@ struct sddmm_plan_s {
     int64_t *d_row_ptr = nullptr;
     WorkItem *d_items = nullptr;
     int64_t n_items = 0;
+    int32_t *d_item_rows = nullptr;  // distinct rows of every item, concatenated
+    int64_t n_item_rows = 0;
     int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
     // staging for host operands (allocated on first use)
     float *d_W = nullptr, *d_H = nullptr, *d_S = nullptr, *d_P = nullptr;
@@ -105,6 +107,7 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_perm);
     cudaFree(p->d_row_ptr);
     cudaFree(p->d_items);
+    cudaFree(p->d_item_rows);
     cudaFree(p->d_W);
     cudaFree(p->d_H);
     cudaFree(p->d_S);
@@ -305,8 +308,8 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
         cols_p = p->d_cols_t;
     }
     PLAN_TRY(build_work_items(rows_p, cols_p, nnz, p->cfg.panel_rows, p->col_tile, p->cfg.item_nnz, &p->d_items,
-                              &p->n_items, s));
-    p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items);
+                              &p->n_items, &p->d_item_rows, &p->n_item_rows, s));
+    p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items + sizeof(int32_t) * (size_t)p->n_item_rows);
     PLAN_TRY(cudaEventRecord(t1, s));
     PLAN_TRY(cudaEventSynchronize(t1));
     PLAN_TRY(cudaEventElapsedTime(&p->plan_ms, t0, t1));
@@ -386,7 +389,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             h->last_error = "SDDMM_FLAG_TILED_ORDER with S values is not supported on a multi-tile plan";
             return SDDMM_INVALID_ARG;
         }
-        CUDA_TRY(h, launch_panel(p->d_items, p->n_items, rows_p, cols_p, perm, dS, dW, dH, dP, p->K, p->cfg,
+        CUDA_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K, p->cfg,
                                  h->sm_count, h->d_status, s));
     }
     CUDA_TRY(h, cudaEventRecord(h->ev1, s));

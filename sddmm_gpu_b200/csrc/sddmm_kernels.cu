@@ -186,6 +186,163 @@ __device__ __forceinline__ float warp_step(const float *__restrict__ Wbase,  // 
 }
 
 // ---------------------------------------------------------------------------
+// Software-pipelined stream of warp steps.
+//
+// A warp walks the chunks  first, first + stride, ...  (< n_chunks) of NB
+// consecutive nonzeros each, starting at nonzero `begin`.  The 128-bit H loads of
+// chunk k+1 are issued before chunk k is consumed, and the row/column indices are
+// fetched two chunks ahead, so that neither the index latency nor the gather
+// latency is exposed between chunks: every warp keeps one or two chunks' worth of
+// H rows (NB x K x 4 bytes each) in flight all the time.
+//
+// The pipelined path is the predicate-free one: full chunks (NB valid nonzeros)
+// of rows that one pass covers exactly (K == L*C*4).  The last, partial chunk
+// and every other K take the general warp_step.
+// ---------------------------------------------------------------------------
+template <int B, int C>
+struct StepBuf {
+    float4 hv[B][C];
+    unsigned wrow[B];  // W row index of each nonzero (panel-local when W is staged)
+};
+
+template <int L, int C, int B>
+__device__ __forceinline__ void issue_h_loads(StepBuf<B, C> &buf, const char *__restrict__ H_lane,
+                                              unsigned row_bytes, int my_row, int my_col, int lane)
+{
+    using S = Shape<L, C, B>;
+    const int g = lane / L;
+#pragma unroll
+    for (int j = 0; j < B; ++j) {
+        const unsigned rj = (unsigned)__shfl_sync(FULL, my_row, j * S::G + g);
+        const unsigned cj = (unsigned)__shfl_sync(FULL, my_col, j * S::G + g);
+        const float4 *hrow = reinterpret_cast<const float4 *>(H_lane + (size_t)cj * row_bytes);
+        buf.wrow[j] = rj;
+#pragma unroll
+        for (int c = 0; c < C; ++c) buf.hv[j][c] = ld_h(hrow + c * L);
+    }
+}
+
+template <int L, int C, int B, bool W_IN_SMEM>
+__device__ __forceinline__ float consume_step(const StepBuf<B, C> &buf, const char *__restrict__ W_lane,
+                                              unsigned row_bytes, int lane)
+{
+    using S = Shape<L, C, B>;
+    const int lig = lane & (L - 1);
+    float acc[B];
+#pragma unroll
+    for (int j = 0; j < B; ++j) {
+        acc[j] = 0.f;
+        // 32-bit offset inside a staged panel, 64-bit into the whole of W otherwise
+        const float4 *wrow = reinterpret_cast<const float4 *>(
+            W_IN_SMEM ? W_lane + buf.wrow[j] * row_bytes : W_lane + (size_t)buf.wrow[j] * row_bytes);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+#ifdef EXP_NO_W
+            const float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+#else
+            const float4 w = W_IN_SMEM ? wrow[c * L] : __ldg(wrow + c * L);
+#endif
+            acc[j] = dot4(w, buf.hv[j][c], acc[j]);
+        }
+    }
+#ifdef EXP_NO_REDUCE
+    float tot = 0.f;
+#pragma unroll
+    for (int j = 0; j < B; ++j) tot += acc[j];
+    return tot;
+#else
+    reduce_transposed<L, B>(acc, lig);
+    const int t_j = lane / S::G, t_g = lane % S::G;
+    const int src = t_g * L + (t_j & (B - 1)) * (L / B);
+    return __shfl_sync(FULL, acc[0], src);
+#endif
+}
+
+// store(off, n_valid, value): lane t < n_valid holds the result of nonzero begin + off + t.
+// IdxT: int for the bounded range of a work item, int64_t for a whole matrix.
+template <int L, int C, int B, bool W_IN_SMEM, class IdxT, class StoreFn>
+__device__ __forceinline__ void warp_stream(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
+                                            int row_bias, const float *__restrict__ Wbase,
+                                            const float *__restrict__ H, int64_t begin, IdxT count, IdxT first,
+                                            IdxT stride, int K4, int lane, StoreFn store)
+{
+    using S = Shape<L, C, B>;
+    const IdxT n_full = count / S::NB;
+    const int tail = (int)(count - n_full * S::NB);
+    rows += begin;
+    cols += begin;
+    // the partial chunk goes to the warp whose turn it would be
+    if (tail > 0 && (n_full % stride) == (first % stride)) {
+        const IdxT off = n_full * S::NB;
+        int r = 0, c = 0;
+        if (lane < tail) {
+            r = __ldcs(rows + off + lane) - row_bias;
+            c = __ldcs(cols + off + lane);
+        }
+        const float res = warp_step<L, C, B, W_IN_SMEM>(Wbase, H, r, c, tail, K4, lane);
+        store(off, tail, res);
+    }
+    if (K4 != S::STRIDE4) {  // rows that one pass does not cover exactly: general step, not pipelined
+        for (IdxT k = first; k < n_full; k += stride) {
+            const IdxT off = k * S::NB;
+            int r = 0, c = 0;
+            if (lane < S::NB) {
+                r = __ldcs(rows + off + lane) - row_bias;
+                c = __ldcs(cols + off + lane);
+            }
+            const float res = warp_step<L, C, B, W_IN_SMEM>(Wbase, H, r, c, S::NB, K4, lane);
+            store(off, S::NB, res);
+        }
+        return;
+    }
+    if (first >= n_full) return;
+
+    const unsigned row_bytes = (unsigned)K4 * 16u;
+    const int lig = lane & (L - 1);
+    const char *H_lane = reinterpret_cast<const char *>(H) + lig * 16;
+    const char *W_lane = reinterpret_cast<const char *>(Wbase) + lig * 16;
+    const int il = lane & (S::NB - 1);  // lanes >= NB re-read a valid index (NB is a power of two)
+    auto load_raw = [&](IdxT k, int &r, int &c) {
+        // past the end the last full chunk is read again (harmless, never consumed)
+        const IdxT kk = k < n_full ? k : n_full - 1;
+        r = __ldcs(rows + kk * S::NB + il) - row_bias;
+        c = __ldcs(cols + kk * S::NB + il);
+    };
+    StepBuf<B, C> bufA, bufB;
+    int r_nx, c_nx;
+    {
+        int r0, c0;
+        load_raw(first, r0, c0);
+        load_raw(first + stride, r_nx, c_nx);
+        issue_h_loads<L, C, B>(bufA, H_lane, row_bytes, r0, c0, lane);
+    }
+    IdxT k = first;
+    while (true) {
+        // bufA holds chunk k; (r_nx, c_nx) are the indices of chunk k + stride
+        {
+            const IdxT k1 = k + stride;
+            const bool more = k1 < n_full;
+            if (more) issue_h_loads<L, C, B>(bufB, H_lane, row_bytes, r_nx, c_nx, lane);
+            load_raw(k1 + stride, r_nx, c_nx);
+            const float res = consume_step<L, C, B, W_IN_SMEM>(bufA, W_lane, row_bytes, lane);
+            store(k * S::NB, S::NB, res);
+            if (!more) break;
+            k = k1;
+        }
+        {
+            const IdxT k1 = k + stride;
+            const bool more = k1 < n_full;
+            if (more) issue_h_loads<L, C, B>(bufA, H_lane, row_bytes, r_nx, c_nx, lane);
+            load_raw(k1 + stride, r_nx, c_nx);
+            const float res = consume_step<L, C, B, W_IN_SMEM>(bufB, W_lane, row_bytes, lane);
+            store(k * S::NB, S::NB, res);
+            if (!more) break;
+            k = k1;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Kernel A: planless gather.  Warps stride over the nonzeros; W rows come from
 // global memory through L1 (row-sorted input makes consecutive nonzeros share them).
 // ---------------------------------------------------------------------------
@@ -199,127 +356,137 @@ sddmm_gather_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict_
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t base = warp * S::NB; base < nnz; base += n_warps * S::NB) {
-        const int64_t rem = nnz - base;
-        const int n_valid = rem < S::NB ? (int)rem : S::NB;
-        int r = 0, c = 0;
+    auto store = [&](int64_t off, int n_valid, float res) {
         if (lane < n_valid) {
-            r = __ldcs(rows + base + lane);
-            c = __ldcs(cols + base + lane);
+            if (sval) res *= __ldcs(sval + off + lane);
+            __stcs(P + off + lane, res);
         }
-        float res = warp_step<L, C, B, false>(W, H, r, c, n_valid, K4, lane);
-        if (lane < n_valid) {
-            if (sval) res *= __ldcs(sval + base + lane);
-            __stcs(P + base + lane, res);
-        }
-    }
+    };
+    warp_stream<L, C, B, false, int64_t>(rows, cols, 0, W, H, 0, nnz, warp, n_warps, K4, lane, store);
 }
 
 // ---------------------------------------------------------------------------
 // Kernel B: row-panel kernel.
+//
+// Persistent CTAs walk the work items (item = blockIdx.x, + gridDim.x, ...).
+// One producer warp stages the W rows an item touches into one of two
+// shared-memory panels with bulk asynchronous copies (TMA) -- slot = row -
+// item.row_begin, one copy per distinct row -- always one item ahead of the
+// NWARPS consumer warps.  full[b] (tx-count mbarrier) tells the consumers that
+// panel b has landed, empty[b] (NWARPS arrivals) tells the producer that every
+// consumer is done with it; nobody waits on a CTA-wide barrier inside the loop,
+// so a warp that finishes its share of an item early moves on to the next one.
+// Every wait is bounded; a wait that gives up raises DEV_MBARRIER_TIMEOUT and the
+// CTA drains and returns.
 // ---------------------------------------------------------------------------
-// Stage the W rows that the nonzeros [begin, begin+count) touch into `buf`
-// (slot = row - row_begin), one bulk copy per distinct row, issued by the lanes
-// of one warp.  Every lane posts the bytes it is about to copy with expect_tx
-// before it issues them; lane 0 arrives last, so the phase cannot complete early.
-__device__ __forceinline__ void stage_panel(const WorkItem &it, const int32_t *__restrict__ rows,
-                                            const float *__restrict__ W, float *buf, uint64_t *bar,
-                                            int K, int lane)
+struct PanelSmem {
+    uint64_t full[2];
+    uint64_t empty[2];
+    int abort_flag;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, unsigned parity, volatile int *abort_flag)
 {
-    const uint32_t row_bytes = (uint32_t)K * 4u;
-    for (int o = lane; o < it.nnz_count; o += 32) {
-        const int64_t i = it.nnz_begin + o;
-        const int r = rows[i];
-        const bool head = (o == 0) || (rows[i - 1] != r);
-        if (head) {
-            mbar_expect_tx(bar, row_bytes);
-            bulk_g2s(buf + (int64_t)(r - it.row_begin) * K, W + (int64_t)r * K, row_bytes, bar);
-        }
+    for (int it = 0; it < MBAR_SPIN_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255) == 255 && *abort_flag) return false;
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
+    return false;
 }
 
 template <int L, int C, int B, int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
 sddmm_panel_kernel(const WorkItem *__restrict__ items, int64_t n_items,
-                   const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
-                   const int32_t *__restrict__ perm, const float *__restrict__ sval,
-                   const float *__restrict__ W, const float *__restrict__ H,
-                   float *__restrict__ P, int K, int panel_floats, int *dev_status)
+                   const int32_t *__restrict__ item_rows, const int32_t *__restrict__ rows,
+                   const int32_t *__restrict__ cols, const int32_t *__restrict__ perm,
+                   const float *__restrict__ sval, const float *__restrict__ W,
+                   const float *__restrict__ H, float *__restrict__ P, int K, int panel_floats,
+                   int *dev_status)
 {
     using S = Shape<L, C, B>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    float *wbuf = reinterpret_cast<float *>(smem_raw);                               // 2 panels
-    uint64_t *bars = reinterpret_cast<uint64_t *>(wbuf + 2 * (size_t)panel_floats);  // 2 barriers
+    float *wbuf = reinterpret_cast<float *>(smem_raw);  // 2 panels
+    PanelSmem *sm = reinterpret_cast<PanelSmem *>(wbuf + 2 * (size_t)panel_floats);
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int K4 = K >> 2;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
+        mbar_init(&sm->full[0], 1);
+        mbar_init(&sm->full[1], 1);
+        mbar_init(&sm->empty[0], NWARPS);
+        mbar_init(&sm->empty[1], NWARPS);
+        sm->abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
+    volatile int *abort_flag = &sm->abort_flag;
+    bool timed_out = false;
 
-    int64_t it_idx = blockIdx.x;
-    if (warp == 0 && it_idx < n_items) {
-        WorkItem it = items[it_idx];
-        stage_panel(it, rows, W, wbuf, &bars[0], K, lane);
-    }
-
-    unsigned phase_bits = 0;   // bit b = parity of the next phase of buffer b
-    bool next_issued = false;  // a prefetch into the other buffer is in flight
-    bool aborted = false;
-    int b = 0;
-    for (; it_idx < n_items; it_idx += gridDim.x, b ^= 1) {
-        const WorkItem it = items[it_idx];
-        const int64_t next_idx = it_idx + gridDim.x;
-        next_issued = next_idx < n_items;
-        if (next_issued && warp == 0) {
-            WorkItem nx = items[next_idx];
-            stage_panel(nx, rows, W, wbuf + (size_t)(b ^ 1) * panel_floats, &bars[b ^ 1], K, lane);
-        }
-        const bool ok = mbar_wait_bounded(&bars[b], (phase_bits >> b) & 1u);
-        if (__syncthreads_or(!ok)) {  // same decision in every thread
-            aborted = true;
-            break;
-        }
-        phase_bits ^= (1u << b);
-
-        const float *wp = wbuf + (size_t)b * panel_floats;
-        for (int off = warp * S::NB; off < it.nnz_count; off += NWARPS * S::NB) {
-            const int rem = it.nnz_count - off;
-            const int n_valid = rem < S::NB ? rem : S::NB;
-            const int64_t base = it.nnz_begin + off;
-            int r = 0, c = 0;
-            if (lane < n_valid) {
-                r = rows[base + lane] - it.row_begin;
-                c = __ldcs(cols + base + lane);
+    if (warp == NWARPS) {
+        // ---- producer warp ----
+        const uint32_t row_bytes = (uint32_t)K * 4u;
+        int n = 0;
+        for (int64_t idx = blockIdx.x; idx < n_items; idx += gridDim.x, ++n) {
+            const int b = n & 1;
+            if (n >= 2) {  // panel b was last used by item n-2: wait until every consumer released it
+                if (!wait_or_abort(&sm->empty[b], ((n - 2) >> 1) & 1u, abort_flag)) { timed_out = true; break; }
             }
-            float res = warp_step<L, C, B, true>(wp, H, r, c, n_valid, K4, lane);
-            if (lane < n_valid) {
-                if (perm) {
-                    const int64_t dst = __ldcs(perm + base + lane);
-                    if (sval) res *= __ldg(sval + dst);
-                    P[dst] = res;
-                } else {
-                    if (sval) res *= __ldcs(sval + base + lane);
-                    __stcs(P + base + lane, res);
+            const WorkItem it = items[idx];
+            float *buf = wbuf + (size_t)b * panel_floats;
+            // it.reserved = offset of the item's distinct-row list, it.n_rows... see binning
+            const int n_list = it.n_rows;
+            for (int e = lane; e < n_list; e += 32) {
+                const int r = __ldg(item_rows + it.list_begin + e);
+                mbar_expect_tx(&sm->full[b], row_bytes);
+                bulk_g2s(buf + (int64_t)(r - it.row_begin) * K, W + (int64_t)r * K, row_bytes, &sm->full[b]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->full[b]);
+        }
+        // before leaving, make sure every copy this warp issued has landed: the
+        // consumers wait for them anyway, except on the abort path
+        if (timed_out) {
+            if (lane == 0) { *abort_flag = 1; atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT); }
+        }
+    } else {
+        // ---- consumer warps ----
+        int n = 0;
+        for (int64_t idx = blockIdx.x; idx < n_items; idx += gridDim.x, ++n) {
+            const int b = n & 1;
+            const WorkItem it = items[idx];
+            if (!wait_or_abort(&sm->full[b], (n >> 1) & 1u, abort_flag)) { timed_out = true; break; }
+            const float *wp = wbuf + (size_t)b * panel_floats;
+            const int64_t begin = it.nnz_begin;
+            auto store = [&](int off, int n_valid, float res) {
+                if (lane < n_valid) {
+                    const int64_t j = begin + off + lane;
+                    if (perm) {
+                        const int64_t dst = __ldcs(perm + j);
+                        if (sval) res *= __ldg(sval + dst);
+                        P[dst] = res;
+                    } else {
+                        if (sval) res *= __ldcs(sval + j);
+                        __stcs(P + j, res);
+                    }
                 }
-            }
+            };
+            warp_stream<L, C, B, true, int>(rows, cols, it.row_begin, wp, H, begin, it.nnz_count, warp, NWARPS, K4,
+                                            lane, store);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->empty[b]);
         }
-        __syncthreads();  // buffer b is free for the item after next
+        if (timed_out && lane == 0) { *abort_flag = 1; atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT); }
     }
-    if (aborted) {
-        // Report, then give the copies that may still be in flight (the panel that
-        // timed out and the prefetch behind it) a bounded chance to land before
-        // this CTA's shared memory is released.
-        if (threadIdx.x == 0) atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT);
-        (void)mbar_wait_bounded(&bars[b], (phase_bits >> b) & 1u);
-        if (next_issued) (void)mbar_wait_bounded(&bars[b ^ 1], (phase_bits >> (b ^ 1)) & 1u);
+    // Copies may only still be in flight on the abort path (otherwise every
+    // issued panel was waited for by the consumers).  Give them a bounded chance
+    // to land before the CTA's shared memory is released.
+    __syncthreads();
+    if (sm->abort_flag && threadIdx.x < 2) {
+        for (int p = 0; p < 2; ++p)
+            for (int it = 0; it < (1 << 12); ++it)
+                if (mbar_try_wait(&sm->full[threadIdx.x], (unsigned)p)) break;
     }
 }
 
@@ -339,10 +506,10 @@ cudaError_t launch_gather_t(const int32_t *rows, const int32_t *cols, const floa
     return cudaGetLastError();
 }
 
-constexpr int PANEL_WARPS = 8;
+constexpr int PANEL_WARPS = 15;  // consumer warps; with the producer warp 16 warps = 4 per SM sub-partition, 128 registers each
 
 template <int L, int C, int B>
-cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t *rows,
+cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t *item_rows, const int32_t *rows,
                            const int32_t *cols, const int32_t *perm, const float *sval,
                            const float *W, const float *H, float *P, int K, const PanelConfig &cfg,
                            int sm_count, int *dev_status, cudaStream_t stream)
@@ -354,8 +521,9 @@ cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t
     if (blocks > n_items) blocks = n_items;
     if (blocks < 1) blocks = 1;
     const int panel_floats = cfg.panel_rows * K;
-    kern<<<(unsigned)blocks, PANEL_WARPS * 32, cfg.smem_bytes, stream>>>(items, n_items, rows, cols, perm, sval, W, H,
-                                                                       P, K, panel_floats, dev_status);
+    kern<<<(unsigned)blocks, (PANEL_WARPS + 1) * 32, cfg.smem_bytes, stream>>>(items, n_items, item_rows, rows, cols,
+                                                                             perm, sval, W, H, P, K, panel_floats,
+                                                                             dev_status);
     return cudaGetLastError();
 }
 
@@ -368,11 +536,11 @@ cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t
         else if ((K) <= 8) { CALL(2, 1, 2); }          \
         else if ((K) <= 16) { CALL(4, 1, 4); }         \
         else if ((K) <= 32) { CALL(8, 1, 8); }         \
-        else if ((K) <= 64) { CALL(16, 1, 16); }       \
-        else if ((K) <= 128) { CALL(32, 1, 16); }      \
-        else if ((K) <= 256) { CALL(32, 2, 8); }       \
-        else if ((K) <= 512) { CALL(32, 4, 4); }       \
-        else { CALL(32, 8, 2); }                       \
+        else if ((K) <= 64) { CALL(16, 1, 8); }        \
+        else if ((K) <= 128) { CALL(32, 1, 8); }       \
+        else if ((K) <= 256) { CALL(32, 2, 4); }       \
+        else if ((K) <= 512) { CALL(32, 4, 2); }       \
+        else { CALL(32, 8, 1); }                       \
     } while (0)
 
 cudaError_t launch_gather(const int32_t *rows, const int32_t *cols, const float *sval, const float *W,
@@ -385,13 +553,13 @@ cudaError_t launch_gather(const int32_t *rows, const int32_t *cols, const float 
     return cudaSuccess;
 }
 
-cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *rows, const int32_t *cols,
-                         const int32_t *perm, const float *sval, const float *W, const float *H, float *P,
+cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *item_rows, const int32_t *rows,
+                         const int32_t *cols, const int32_t *perm, const float *sval, const float *W, const float *H, float *P,
                          int K, const PanelConfig &cfg, int sm_count, int *dev_status, cudaStream_t stream)
 {
     if (n_items == 0) return cudaSuccess;
 #define CALL(L, C, B) \
-    return launch_panel_t<L, C, B>(items, n_items, rows, cols, perm, sval, W, H, P, K, cfg, sm_count, dev_status, stream)
+    return launch_panel_t<L, C, B>(items, n_items, item_rows, rows, cols, perm, sval, W, H, P, K, cfg, sm_count, dev_status, stream)
     SDDMM_DISPATCH_K(K, CALL);
 #undef CALL
     return cudaSuccess;
@@ -401,26 +569,23 @@ PanelConfig choose_panel_config(int K, int panel_rows_hint, int sm_count, size_t
 {
     (void)sm_count;
     PanelConfig cfg;
-    // Two W panels per CTA.  32 KB panels let three 8-warp CTAs share an SM
-    // (3 x (64 KB + barriers) < 227 KB) while a panel still holds 32 rows at K = 256.
-    size_t panel_bytes = 32 * 1024;
+    // One persistent CTA per SM: 15 consumer warps + 1 producer warp, two W
+    // panels of up to 48 KB each (48 rows at K = 256).
+    size_t panel_bytes = 48 * 1024;
     const size_t row_bytes = (size_t)K * 4;
     if (row_bytes * 2 > panel_bytes) panel_bytes = row_bytes * 2;  // at least two rows per panel
     int rows = (int)(panel_bytes / row_bytes);
     if (panel_rows_hint > 0 && panel_rows_hint < rows) rows = panel_rows_hint;
     if (rows < 1) rows = 1;
     cfg.panel_rows = rows;
-    cfg.smem_bytes = 2 * (size_t)rows * row_bytes + 64;
+    cfg.smem_bytes = 2 * (size_t)rows * row_bytes + 128;
     while (cfg.smem_bytes > smem_optin && cfg.panel_rows > 1) {
         cfg.panel_rows /= 2;
-        cfg.smem_bytes = 2 * (size_t)cfg.panel_rows * row_bytes + 64;
+        cfg.smem_bytes = 2 * (size_t)cfg.panel_rows * row_bytes + 128;
     }
-    cfg.threads = PANEL_WARPS * 32;
-    int per_sm = (int)((smem_optin + 1024) / (cfg.smem_bytes + 1024));
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 3) per_sm = 3;
-    cfg.ctas_per_sm = per_sm;
-    cfg.item_nnz = 2048;
+    cfg.threads = (PANEL_WARPS + 1) * 32;
+    cfg.ctas_per_sm = 1;
+    cfg.item_nnz = 4096;
     return cfg;
 }
 
