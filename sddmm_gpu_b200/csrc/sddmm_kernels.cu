@@ -188,12 +188,18 @@ __device__ __forceinline__ float warp_step(const float *__restrict__ Wbase,  // 
 // ---------------------------------------------------------------------------
 // Software-pipelined stream of warp steps.
 //
-// A warp walks the chunks  first, first + stride, ...  (< n_chunks) of NB
-// consecutive nonzeros each, starting at nonzero `begin`.  The 128-bit H loads of
-// chunk k+1 are issued before chunk k is consumed, and the row/column indices are
-// fetched two chunks ahead, so that neither the index latency nor the gather
-// latency is exposed between chunks: every warp keeps one or two chunks' worth of
-// H rows (NB x K x 4 bytes each) in flight all the time.
+// The nonzeros [begin, begin + count) are cut into chunks of NB consecutive
+// nonzeros; warp `part` of `n_parts` takes a contiguous range of chunks.  The
+// 128-bit H loads of chunk k+1 are issued before chunk k is consumed, and the
+// row/column indices are fetched two chunks ahead, so that neither the index
+// latency nor the gather latency is exposed between chunks: every warp keeps one
+// or two chunks' worth of H rows (NB x K x 4 bytes each) in flight all the time.
+//
+// Consecutive chunks of a warp mostly lie in one row of S (rows are sorted and
+// most nonzeros sit in long rows).  A chunk whose nonzeros all share a row takes
+// that row of W from registers: it is (re)loaded only when the row changes, so
+// the per-nonzero work is the H gather, K FMAs and the reduction.  Mixed chunks
+// read W per nonzero (from the staged panel, or from global memory).
 //
 // The pipelined path is the predicate-free one: full chunks (NB valid nonzeros)
 // of rows that one pass covers exactly (K == L*C*4).  The last, partial chunk
@@ -202,7 +208,15 @@ __device__ __forceinline__ float warp_step(const float *__restrict__ Wbase,  // 
 template <int B, int C>
 struct StepBuf {
     float4 hv[B][C];
-    unsigned wrow[B];  // W row index of each nonzero (panel-local when W is staged)
+    int my_row;   // row of nonzero `lane` of the chunk (lanes >= NB mirror a valid one)
+    int row0;     // row of the chunk's first nonzero
+    bool single;  // every nonzero of the chunk lies in row0
+};
+
+template <int C>
+struct WCache {
+    float4 w[C];
+    int row;  // row held in w, -1 if none
 };
 
 template <int L, int C, int B>
@@ -211,51 +225,60 @@ __device__ __forceinline__ void issue_h_loads(StepBuf<B, C> &buf, const char *__
 {
     using S = Shape<L, C, B>;
     const int g = lane / L;
+    buf.my_row = my_row;
+    buf.row0 = __shfl_sync(FULL, my_row, 0);
+    buf.single = __all_sync(FULL, my_row == buf.row0);
 #pragma unroll
     for (int j = 0; j < B; ++j) {
-        const unsigned rj = (unsigned)__shfl_sync(FULL, my_row, j * S::G + g);
         const unsigned cj = (unsigned)__shfl_sync(FULL, my_col, j * S::G + g);
         const float4 *hrow = reinterpret_cast<const float4 *>(H_lane + (size_t)cj * row_bytes);
-        buf.wrow[j] = rj;
 #pragma unroll
         for (int c = 0; c < C; ++c) buf.hv[j][c] = ld_h(hrow + c * L);
     }
 }
 
 template <int L, int C, int B, bool W_IN_SMEM>
-__device__ __forceinline__ float consume_step(const StepBuf<B, C> &buf, const char *__restrict__ W_lane,
-                                              unsigned row_bytes, int lane)
+__device__ __forceinline__ float consume_step(const StepBuf<B, C> &buf, WCache<C> &wc,
+                                              const char *__restrict__ W_lane, unsigned row_bytes, int lane)
 {
     using S = Shape<L, C, B>;
     const int lig = lane & (L - 1);
+    const int g = lane / L;
     float acc[B];
+    // 32-bit offset inside a staged panel, 64-bit into the whole of W otherwise
+    auto w_row_ptr = [&](unsigned r) {
+        return reinterpret_cast<const float4 *>(W_IN_SMEM ? W_lane + r * row_bytes : W_lane + (size_t)r * row_bytes);
+    };
+    if (buf.single) {
+        if (buf.row0 != wc.row) {
+            const float4 *wrow = w_row_ptr((unsigned)buf.row0);
 #pragma unroll
-    for (int j = 0; j < B; ++j) {
-        acc[j] = 0.f;
-        // 32-bit offset inside a staged panel, 64-bit into the whole of W otherwise
-        const float4 *wrow = reinterpret_cast<const float4 *>(
-            W_IN_SMEM ? W_lane + buf.wrow[j] * row_bytes : W_lane + (size_t)buf.wrow[j] * row_bytes);
+            for (int c = 0; c < C; ++c) wc.w[c] = W_IN_SMEM ? wrow[c * L] : __ldg(wrow + c * L);
+            wc.row = buf.row0;
+        }
 #pragma unroll
-        for (int c = 0; c < C; ++c) {
-#ifdef EXP_NO_W
-            const float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
-#else
-            const float4 w = W_IN_SMEM ? wrow[c * L] : __ldg(wrow + c * L);
-#endif
-            acc[j] = dot4(w, buf.hv[j][c], acc[j]);
+        for (int j = 0; j < B; ++j) {
+            acc[j] = 0.f;
+#pragma unroll
+            for (int c = 0; c < C; ++c) acc[j] = dot4(wc.w[c], buf.hv[j][c], acc[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            acc[j] = 0.f;
+            const unsigned rj = (unsigned)__shfl_sync(FULL, buf.my_row, j * S::G + g);
+            const float4 *wrow = w_row_ptr(rj);
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const float4 w = W_IN_SMEM ? wrow[c * L] : __ldg(wrow + c * L);
+                acc[j] = dot4(w, buf.hv[j][c], acc[j]);
+            }
         }
     }
-#ifdef EXP_NO_REDUCE
-    float tot = 0.f;
-#pragma unroll
-    for (int j = 0; j < B; ++j) tot += acc[j];
-    return tot;
-#else
     reduce_transposed<L, B>(acc, lig);
     const int t_j = lane / S::G, t_g = lane % S::G;
     const int src = t_g * L + (t_j & (B - 1)) * (L / B);
     return __shfl_sync(FULL, acc[0], src);
-#endif
 }
 
 // store(off, n_valid, value): lane t < n_valid holds the result of nonzero begin + off + t.
@@ -263,16 +286,15 @@ __device__ __forceinline__ float consume_step(const StepBuf<B, C> &buf, const ch
 template <int L, int C, int B, bool W_IN_SMEM, class IdxT, class StoreFn>
 __device__ __forceinline__ void warp_stream(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
                                             int row_bias, const float *__restrict__ Wbase,
-                                            const float *__restrict__ H, int64_t begin, IdxT count, IdxT first,
-                                            IdxT stride, int K4, int lane, StoreFn store)
+                                            const float *__restrict__ H, int64_t begin, IdxT count, IdxT part,
+                                            IdxT n_parts, int K4, int lane, StoreFn store)
 {
     using S = Shape<L, C, B>;
     const IdxT n_full = count / S::NB;
     const int tail = (int)(count - n_full * S::NB);
     rows += begin;
     cols += begin;
-    // the partial chunk goes to the warp whose turn it would be
-    if (tail > 0 && (n_full % stride) == (first % stride)) {
+    if (tail > 0 && part == n_parts - 1) {  // the partial chunk
         const IdxT off = n_full * S::NB;
         int r = 0, c = 0;
         if (lane < tail) {
@@ -282,8 +304,12 @@ __device__ __forceinline__ void warp_stream(const int32_t *__restrict__ rows, co
         const float res = warp_step<L, C, B, W_IN_SMEM>(Wbase, H, r, c, tail, K4, lane);
         store(off, tail, res);
     }
+    // this warp's contiguous share of the full chunks
+    IdxT k = (IdxT)(((int64_t)n_full * part) / n_parts);
+    const IdxT k_end = (IdxT)(((int64_t)n_full * (part + 1)) / n_parts);
+    if (k >= k_end) return;
     if (K4 != S::STRIDE4) {  // rows that one pass does not cover exactly: general step, not pipelined
-        for (IdxT k = first; k < n_full; k += stride) {
+        for (; k < k_end; ++k) {
             const IdxT off = k * S::NB;
             int r = 0, c = 0;
             if (lane < S::NB) {
@@ -295,49 +321,47 @@ __device__ __forceinline__ void warp_stream(const int32_t *__restrict__ rows, co
         }
         return;
     }
-    if (first >= n_full) return;
 
     const unsigned row_bytes = (unsigned)K4 * 16u;
     const int lig = lane & (L - 1);
     const char *H_lane = reinterpret_cast<const char *>(H) + lig * 16;
     const char *W_lane = reinterpret_cast<const char *>(Wbase) + lig * 16;
-    const int il = lane & (S::NB - 1);  // lanes >= NB re-read a valid index (NB is a power of two)
-    auto load_raw = [&](IdxT k, int &r, int &c) {
-        // past the end the last full chunk is read again (harmless, never consumed)
-        const IdxT kk = k < n_full ? k : n_full - 1;
+    const int il = lane & (S::NB - 1);  // lanes >= NB mirror a valid nonzero (NB is a power of two)
+    auto load_raw = [&](IdxT kk, int &r, int &c) {
+        // past the end the last chunk is read again (harmless, never consumed)
+        if (kk >= k_end) kk = k_end - 1;
         r = __ldcs(rows + kk * S::NB + il) - row_bias;
         c = __ldcs(cols + kk * S::NB + il);
     };
     StepBuf<B, C> bufA, bufB;
+    WCache<C> wc;
+    wc.row = -1;
     int r_nx, c_nx;
     {
         int r0, c0;
-        load_raw(first, r0, c0);
-        load_raw(first + stride, r_nx, c_nx);
+        load_raw(k, r0, c0);
+        load_raw(k + 1, r_nx, c_nx);
         issue_h_loads<L, C, B>(bufA, H_lane, row_bytes, r0, c0, lane);
     }
-    IdxT k = first;
     while (true) {
-        // bufA holds chunk k; (r_nx, c_nx) are the indices of chunk k + stride
+        // bufA holds chunk k; (r_nx, c_nx) are the indices of chunk k + 1
         {
-            const IdxT k1 = k + stride;
-            const bool more = k1 < n_full;
+            const bool more = k + 1 < k_end;
             if (more) issue_h_loads<L, C, B>(bufB, H_lane, row_bytes, r_nx, c_nx, lane);
-            load_raw(k1 + stride, r_nx, c_nx);
-            const float res = consume_step<L, C, B, W_IN_SMEM>(bufA, W_lane, row_bytes, lane);
+            load_raw(k + 2, r_nx, c_nx);
+            const float res = consume_step<L, C, B, W_IN_SMEM>(bufA, wc, W_lane, row_bytes, lane);
             store(k * S::NB, S::NB, res);
             if (!more) break;
-            k = k1;
+            ++k;
         }
         {
-            const IdxT k1 = k + stride;
-            const bool more = k1 < n_full;
+            const bool more = k + 1 < k_end;
             if (more) issue_h_loads<L, C, B>(bufA, H_lane, row_bytes, r_nx, c_nx, lane);
-            load_raw(k1 + stride, r_nx, c_nx);
-            const float res = consume_step<L, C, B, W_IN_SMEM>(bufB, W_lane, row_bytes, lane);
+            load_raw(k + 2, r_nx, c_nx);
+            const float res = consume_step<L, C, B, W_IN_SMEM>(bufB, wc, W_lane, row_bytes, lane);
             store(k * S::NB, S::NB, res);
             if (!more) break;
-            k = k1;
+            ++k;
         }
     }
 }
