@@ -54,7 +54,7 @@ def parse_args():
     ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--k", type=int, default=0, help="override K of the workload")
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (c3/c4), for quick runs")
-    ap.add_argument("--kernel", default="panel", choices=["panel", "gather"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "panel", "gather"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
@@ -284,7 +284,9 @@ def main():
     stream = torch.cuda.Stream(device=device)
     torch.cuda.set_stream(stream)
     handle.set_stream(stream.cuda_stream)
-    kflag = api.FLAG_KERNEL_GATHER if args.kernel == "gather" else api.FLAG_KERNEL_PANEL
+    kflag = {"auto": 0, "ring": api.FLAG_KERNEL_RING, "panel": api.FLAG_KERNEL_PANEL,
+             "gather": api.FLAG_KERNEL_GATHER}[args.kernel]
+    kernel_name = args.kernel if args.kernel != "auto" else ("ring" if K in (128, 256, 512, 1024) else "panel")
 
     # ---- sharding (identity at one GPU) --------------------------------------
     rows_host = rows.cpu().numpy()
@@ -347,7 +349,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": alg_bytes,
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(step_ms),
-                "kernel": f"sddmm_{args.kernel}_kernel"}
+                "kernel": f"sddmm_{kernel_name}_kernel"}
     if traffic:
         roofline["dram_gbs"] = traffic / (kernel_ms * 1e-3) / 1e9
         roofline["dram_frac"] = roofline["dram_gbs"] / peak
@@ -437,7 +439,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": p["workload"], "M": M, "N": N, "nnz": nnz, "K": K,
                        "l2": "inputs larger than L2 (no flush)" if 4 * K * (M + N) > 200e6 else "inputs fit L2",
-                       "parallelism": f"nnz-balanced row blocks x{world}", "kernel": args.kernel,
+                       "parallelism": f"nnz-balanced row blocks x{world}", "kernel": kernel_name,
                        "panel_rows": info.panel_rows, "work_items": info.n_work_items,
                        "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,

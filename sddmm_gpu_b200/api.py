@@ -22,6 +22,7 @@ FLAG_ASYNC = 0x1
 FLAG_TILED_ORDER = 0x2
 FLAG_KERNEL_GATHER = 0x10
 FLAG_KERNEL_PANEL = 0x20
+FLAG_KERNEL_RING = 0x40
 PLAN_SKIP_VALIDATION = 0x1
 PLAN_DEVICE_INDICES = 0x2
 

@@ -5,6 +5,7 @@
 // assert(), and there is exactly one kernel launch per execute.
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -24,6 +25,7 @@ struct sddmm_handle_s {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int *d_status = nullptr;  // device status word of bounded waits
+    unsigned long long *d_work_counter = nullptr;  // dynamic work distribution of the ring kernel
     int *h_status = nullptr;  // pinned mirror
     std::string last_error;
 };
@@ -178,6 +180,7 @@ int sddmm_create(sddmm_handle_t *out, int device)
     if (e == cudaSuccess) e = cudaEventCreate(&h->ev1);
     if (e == cudaSuccess) e = cudaMalloc((void **)&h->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&h->d_work_counter, sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaHostAlloc((void **)&h->h_status, sizeof(int), cudaHostAllocDefault);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -198,6 +201,7 @@ int sddmm_destroy(sddmm_handle_t h)
     if (h->ev0) cudaEventDestroy(h->ev0);
     if (h->ev1) cudaEventDestroy(h->ev1);
     if (h->d_status) cudaFree(h->d_status);
+    if (h->d_work_counter) cudaFree(h->d_work_counter);
     if (h->h_status) cudaFreeHost(h->h_status);
     (void)cudaGetLastError();
     delete h;
@@ -339,7 +343,10 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     if (!W || !H || !P) return SDDMM_INVALID_ARG;
     const bool use_gather = (flags & SDDMM_FLAG_KERNEL_GATHER) != 0;
     const bool tiled_out = (flags & SDDMM_FLAG_TILED_ORDER) != 0;
-    if (use_gather && (flags & SDDMM_FLAG_KERNEL_PANEL)) return SDDMM_INVALID_ARG;
+    const uint32_t forced = flags & (SDDMM_FLAG_KERNEL_GATHER | SDDMM_FLAG_KERNEL_PANEL | SDDMM_FLAG_KERNEL_RING);
+    if (forced & (forced - 1)) return SDDMM_INVALID_ARG;  // at most one kernel may be forced
+    if ((flags & SDDMM_FLAG_KERNEL_RING) && !ring_supports(p->K)) return SDDMM_K_UNSUPPORTED;
+    const bool use_ring = (flags & SDDMM_FLAG_KERNEL_RING) || (!forced && ring_supports(p->K));
     if (use_gather && tiled_out && p->d_perm) return SDDMM_INVALID_ARG;
     CUDA_TRY(h, cudaSetDevice(h->device));
     cudaStream_t s = h->stream;
@@ -373,6 +380,11 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         dP = p->d_P;
     }
 
+    // every kernel moves 16-byte vectors
+    if ((((uintptr_t)dW | (uintptr_t)dH) & 15u) != 0) {
+        h->last_error = "W and H must be 16-byte aligned on the device";
+        return SDDMM_INVALID_ARG;
+    }
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (use_gather) {
         CUDA_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
@@ -389,8 +401,12 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             h->last_error = "SDDMM_FLAG_TILED_ORDER with S values is not supported on a multi-tile plan";
             return SDDMM_INVALID_ARG;
         }
-        CUDA_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K, p->cfg,
-                                 h->sm_count, h->d_status, s));
+        if (use_ring)
+            CUDA_TRY(h, launch_ring(rows_p, cols_p, perm, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, h->d_work_counter,
+                                    h->d_status, s));
+        else
+            CUDA_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K,
+                                     p->cfg, h->sm_count, h->d_status, s));
     }
     CUDA_TRY(h, cudaEventRecord(h->ev1, s));
     if (!p_dev) CUDA_TRY(h, cudaMemcpyAsync(P, dP, nbytes, cudaMemcpyDeviceToHost, s));

@@ -14,7 +14,12 @@ from sddmm_gpu_b200 import api, synth
 
 pytestmark = pytest.mark.gpu
 
-KERNELS = {"panel": api.FLAG_KERNEL_PANEL, "gather": api.FLAG_KERNEL_GATHER}
+KERNELS = {"panel": api.FLAG_KERNEL_PANEL, "gather": api.FLAG_KERNEL_GATHER, "ring": api.FLAG_KERNEL_RING}
+RING_K = (128, 256, 512, 1024)
+
+
+def kernels_for(K):
+    return [k for k in KERNELS if k != "ring" or K in RING_K]
 
 
 def run_plan(engine, M, N, rows, cols, W, H, vals=None, flags=0, panel_rows=0, col_tile=0):
@@ -34,7 +39,7 @@ def test_hand_computable(engine):
     W = np.arange(12, dtype=np.float32).reshape(3, 4)
     H = (np.arange(16, dtype=np.float32).reshape(4, 4) % 5) - 2
     expect = np.array([(W[r] * H[c]).sum() for r, c in zip(rows, cols)], np.float32)
-    for flag in KERNELS.values():
+    for flag in (KERNELS["panel"], KERNELS["gather"], 0):
         P, _ = run_plan(engine, 3, 4, rows, cols, W, H, None, flag)
         assert np.array_equal(P, expect)
         P, _ = run_plan(engine, 3, 4, rows, cols, W, H, vals, flag)
@@ -44,6 +49,8 @@ def test_hand_computable(engine):
 @pytest.mark.parametrize("kernel", list(KERNELS))
 @pytest.mark.parametrize("K", [4, 8, 12, 16, 20, 32, 36, 64, 100, 128, 192, 256, 260, 512, 1024, 2048])
 def test_every_k(engine, kernel, K):
+    if kernel not in kernels_for(K):
+        pytest.skip("the ring kernel covers K = 128, 256, 512, 1024")
     rng = np.random.default_rng(K)
     M, N = 257, 190
     rows, cols = random_coo(rng, M, N, 6000, empty_rows=[0, 5, 6, 7, 100, 256])
@@ -59,7 +66,7 @@ def test_every_k(engine, kernel, K):
 @pytest.mark.parametrize("kernel", list(KERNELS))
 def test_structure_edge_cases(engine, kernel):
     rng = np.random.default_rng(7)
-    K = 32
+    K = 128 if kernel == "ring" else 32
     flag = KERNELS[kernel]
     cases = []
     # nnz = 1, M = 1, N = 1, max column index, one row holding everything
@@ -127,12 +134,13 @@ def test_validation_errors(engine):
     plan.close()
 
 
+@pytest.mark.parametrize("K", [64, 128])
 @pytest.mark.parametrize("col_tile,panel_rows", [(64, 16), (33, 7), (1, 1), (500, 192), (128, 0)])
-def test_column_tiled_plan(engine, col_tile, panel_rows):
+def test_column_tiled_plan(engine, col_tile, panel_rows, K):
     # a multi-tile plan processes in the reference's tiled order and still
     # returns P in input order; TILED_ORDER returns what sddmm_GPU leaves in d_val
     rng = np.random.default_rng(11)
-    M, N, K = 300, 200, 64
+    M, N = 300, 200
     rows, cols = random_coo(rng, M, N, 5003)
     vals = rng.integers(1, 20, rows.shape[0]).astype(np.float32)
     W = rng.random((M, K), dtype=np.float32)
@@ -190,6 +198,8 @@ def test_benchmark_configs(engine, name, kernel):
         p = _scaled(synth.rmat, scale=15, edge_factor=24, K=256, seed=synth.SEEDS["c4"])
     else:
         p = _scaled(synth.attention_mask, M=4096, half_width=64, n_global=12, K=64)
+    if kernel not in kernels_for(p["K"]):
+        pytest.skip("the ring kernel covers K = 128, 256, 512, 1024")
     P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], KERNELS[kernel],
                        p["panel_rows"], p["col_tile"])
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
@@ -227,8 +237,9 @@ def test_linearity_at_scale(engine):
     plan.execute(p["W"] + W2, p["H"], P3)
     scale = (p["W"].abs().max() + W2.abs().max()) * p["H"].abs().max() * p["K"]
     assert float((P1 + P2 - P3).abs().max()) <= 1e-5 * float(scale)
-    # and both kernels agree with each other to rounding
-    P4 = torch.empty(nnz, device="cuda")
-    plan.execute(p["W"], p["H"], P4, None, api.FLAG_KERNEL_GATHER)
-    assert float((P1 - P4).abs().max()) <= 1e-5 * float(scale)
+    # and the kernels agree with each other to rounding
+    for flag in KERNELS.values():
+        P4 = torch.empty(nnz, device="cuda")
+        plan.execute(p["W"], p["H"], P4, None, flag)
+        assert float((P1 - P4).abs().max()) <= 1e-5 * float(scale)
     plan.close()
