@@ -38,19 +38,29 @@ using namespace dev;
 
 namespace {
 
-constexpr int RING_WARPS = 16;
-constexpr int RING_NG = 3;            // ring slots (groups) per warp
-constexpr int RING_GROUP_BYTES = 4096;
+#ifndef SDDMM_RING_WARPS
+#define SDDMM_RING_WARPS 24
+#endif
+#ifndef SDDMM_RING_NG
+#define SDDMM_RING_NG 2
+#endif
+#ifndef SDDMM_RING_GROUP_BYTES
+#define SDDMM_RING_GROUP_BYTES 4096
+#endif
+constexpr int RING_WARPS = SDDMM_RING_WARPS;
+constexpr int RING_NG = SDDMM_RING_NG;  // ring slots (groups) per warp
+constexpr int RING_GROUP_BYTES = SDDMM_RING_GROUP_BYTES;
 constexpr int RING_BLOCK_GROUPS = 128;  // groups per dynamically scheduled block
 
 template <int C>
 struct RingShape {
     static constexpr int ROW_BYTES = C * 512;
-    static constexpr int B = RING_GROUP_BYTES / ROW_BYTES;  // nonzeros per group
+    static constexpr int SLOT_BYTES = RING_GROUP_BYTES > ROW_BYTES ? RING_GROUP_BYTES : ROW_BYTES;
+    static constexpr int B = SLOT_BYTES / ROW_BYTES;  // nonzeros per group
     static_assert(B >= 1 && B <= 32, "group size");
 };
 
-template <int C>
+template <int C, bool HAS_PERM, bool HAS_SVAL>
 __global__ void __launch_bounds__(RING_WARPS * 32, 1)
 sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
                   const int32_t *__restrict__ perm, const float *__restrict__ sval,
@@ -64,9 +74,9 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    // per warp: NG groups of 4 KB, then (after all rings) NG mbarriers per warp
-    unsigned char *ring = smem_raw + (size_t)warp * NG * RING_GROUP_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)RING_WARPS * NG * RING_GROUP_BYTES) + warp * NG;
+    // per warp: NG slots of one group each, then (after all rings) NG mbarriers per warp
+    unsigned char *ring = smem_raw + (size_t)warp * NG * R::SLOT_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)RING_WARPS * NG * R::SLOT_BYTES) + warp * NG;
     if (lane < NG) mbar_init(&bars[lane], 1);
     mbar_fence_init();
     __syncwarp();
@@ -77,10 +87,46 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     const char *W_lane = reinterpret_cast<const char *>(W) + lane * 16;
     const int il = lane & (B - 1);  // lanes >= B mirror a valid nonzero of the group
 
-    unsigned n_issued = 0, n_consumed = 0;  // groups this warp has issued / consumed since the kernel began
+    // Ring bookkeeping.  Issue and consume each walk the NG slots round-robin; a
+    // slot's mbarrier phase flips every time the slot is reused, so the parity to
+    // wait for is the number of completed walks of the consumer, modulo 2.
+    unsigned s_issue = 0, s_cons = 0;  // next slot to issue into / to consume
+    unsigned cons_parity = 0;          // parity of the consumer's current walk
+    unsigned in_flight = 0;            // groups issued and not yet consumed
     bool timed_out = false;
-    float4 wc[C];   // W row of a single-row group
+    float4 wc[C];  // W row of a single-row group
     int wc_row = -1;
+
+    // One lane arms the slot's mbarrier with the byte count and issues the B row
+    // copies (column indices arrive by shuffle, so the issuing code is uniform).
+    auto issue = [&](int c_mine) {
+        unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
+        uint64_t *bar = &bars[s_issue];
+        unsigned cj[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j) cj[j] = (unsigned)__shfl_sync(FULL, c_mine, j);
+        if (lane == 0) {
+            asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(
+                             smem_u32(bar)),
+                         "r"((unsigned)(B * R::ROW_BYTES))
+                         : "memory");
+#pragma unroll
+            for (int j = 0; j < B; ++j)
+                bulk_g2s(slot + j * R::ROW_BYTES, Hb + (size_t)cj[j] * R::ROW_BYTES, R::ROW_BYTES, bar);
+        }
+        s_issue = (s_issue + 1 == NG) ? 0 : s_issue + 1;
+        ++in_flight;
+    };
+    auto store = [&](int64_t j, float v) {
+        if (HAS_PERM) {
+            const int64_t dst = __ldcs(perm + j);
+            if (HAS_SVAL) v *= __ldg(sval + dst);
+            P[dst] = v;
+        } else {
+            if (HAS_SVAL) v *= __ldcs(sval + j);
+            __stcs(P + j, v);
+        }
+    };
 
     while (!timed_out) {
         unsigned long long blk = 0;
@@ -97,42 +143,24 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
                     r = __ldcs(rows + off + lane);
                     c = __ldcs(cols + off + lane);
                 }
-                float res = warp_step<32, C, B, false>(W, H, r, c, tail, K4, lane);
-                if (lane < tail) {
-                    const int64_t j = off + lane;
-                    const int64_t dst = perm ? (int64_t)__ldcs(perm + j) : j;
-                    if (sval) res *= __ldg(sval + dst);
-                    P[dst] = res;
-                }
+                const float res = warp_step<32, C, B, false>(W, H, r, c, tail, K4, lane);
+                if (lane < tail) store(off + lane, res);
             }
             continue;
         }
         const int64_t g0 = (int64_t)blk * RING_BLOCK_GROUPS;
         const int n = (int)((n_groups - g0) < RING_BLOCK_GROUPS ? (n_groups - g0) : RING_BLOCK_GROUPS);
-        const int32_t *brow = rows + g0 * B;
-        const int32_t *bcol = cols + g0 * B;
+        const int32_t *brow = rows + g0 * B + il;
+        const int32_t *bcol = cols + g0 * B + il;
 
         // (row, col) of nonzero `il` of group q of this block; past the end the last group is re-read
         auto load_idx = [&](int q, int &r, int &c) {
             const int qq = q < n ? q : n - 1;
-            r = __ldcs(brow + qq * B + il);
-            c = __ldcs(bcol + qq * B + il);
-        };
-        auto issue = [&](int c_mine) {
-            const unsigned s = n_issued % NG;
-            if (lane == 0) {
-                asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(
-                                 smem_u32(&bars[s])),
-                             "r"((unsigned)(B * R::ROW_BYTES))
-                             : "memory");
-            }
-            if (lane < B)
-                bulk_g2s(ring + s * RING_GROUP_BYTES + lane * R::ROW_BYTES, Hb + (size_t)(unsigned)c_mine * R::ROW_BYTES,
-                         R::ROW_BYTES, &bars[s]);
-            ++n_issued;
+            r = __ldcs(brow + qq * B);
+            c = __ldcs(bcol + qq * B);
         };
 
-        // index registers of the groups in flight: r_q[i], c_q[i] belong to group (cur + i)
+        // index registers of the groups ahead: r_q[i], c_q[i] belong to group (current + i)
         int r_q[NG], c_q[NG];
 #pragma unroll
         for (int i = 0; i < NG; ++i) load_idx(i, r_q[i], c_q[i]);
@@ -141,42 +169,36 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         for (int i = 0; i < NG - 1; ++i)
             if (i < n) issue(c_q[i]);
 
-        // W of the first group
-        float4 wm[B][C];  // W rows of a group that straddles rows
+        // W of the next group: a group whose nonzeros share one row keeps that row
+        // of W in registers (fetched here, one group ahead, only when the row
+        // changes); a group that straddles rows reads W per nonzero when consumed.
         auto prefetch_w = [&](int r_mine) {
             const int r0 = __shfl_sync(FULL, r_mine, 0);
             const bool single = __all_sync(FULL, r_mine == r0);
-            if (single) {
-                if (r0 != wc_row) {
-                    const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)(unsigned)r0 * R::ROW_BYTES);
+            if (single && r0 != wc_row) {
+                const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)(unsigned)r0 * R::ROW_BYTES);
 #pragma unroll
-                    for (int c = 0; c < C; ++c) wc[c] = __ldg(wrow + c * 32);
-                    wc_row = r0;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    const unsigned rj = (unsigned)__shfl_sync(FULL, r_mine, j);
-                    const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)rj * R::ROW_BYTES);
-#pragma unroll
-                    for (int c = 0; c < C; ++c) wm[j][c] = __ldg(wrow + c * 32);
-                }
+                for (int c = 0; c < C; ++c) wc[c] = __ldg(wrow + c * 32);
+                wc_row = r0;
             }
             return single;
         };
         bool single = prefetch_w(r_q[0]);
 
         for (int q = 0; q < n; ++q) {
-            // keep NG-1 groups in flight: issue group q + NG - 1 into the slot freed by group q - 1
+            // keep NG-1 groups in flight: group q + NG - 1 goes into the slot freed by group q - 1
             if (q + NG - 1 < n) issue(c_q[NG - 1]);
             // wait for group q
-            const unsigned s = n_consumed % NG;
-            if (!mbar_wait_bounded(&bars[s], (n_consumed / NG) & 1u)) {
+            if (!mbar_try_wait(&bars[s_cons], cons_parity) && !mbar_wait_bounded(&bars[s_cons], cons_parity)) {
                 timed_out = true;
                 break;
             }
-            ++n_consumed;
-            const float4 *slot = reinterpret_cast<const float4 *>(ring + s * RING_GROUP_BYTES) + lane;
+            const float4 *slot = reinterpret_cast<const float4 *>(ring + s_cons * R::SLOT_BYTES) + lane;
+            --in_flight;
+            if (++s_cons == NG) {
+                s_cons = 0;
+                cons_parity ^= 1u;
+            }
             float acc[B];
             if (single) {
 #pragma unroll
@@ -189,8 +211,10 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
 #pragma unroll
                 for (int j = 0; j < B; ++j) {
                     acc[j] = 0.f;
+                    const unsigned rj = (unsigned)__shfl_sync(FULL, r_q[0], j);
+                    const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)rj * R::ROW_BYTES);
 #pragma unroll
-                    for (int c = 0; c < C; ++c) acc[j] = dot4(wm[j][c], slot[j * K4 + c * 32], acc[j]);
+                    for (int c = 0; c < C; ++c) acc[j] = dot4(__ldg(wrow + c * 32), slot[j * K4 + c * 32], acc[j]);
                 }
             }
             // shift the index queue, fetch the indices of group q + NG, prefetch W of group q + 1
@@ -205,18 +229,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
             // reduce, route, store
             reduce_transposed<32, B>(acc, lane);
             const float res = __shfl_sync(FULL, acc[0], (lane & (B - 1)) * (32 / B));
-            if (lane < B) {
-                const int64_t j = (g0 + q) * B + lane;
-                float v = res;
-                if (perm) {
-                    const int64_t dst = __ldcs(perm + j);
-                    if (sval) v *= __ldg(sval + dst);
-                    P[dst] = v;
-                } else {
-                    if (sval) v *= __ldcs(sval + j);
-                    __stcs(P + j, v);
-                }
-            }
+            if (lane < B) store((g0 + q) * B + lane, res);
             single = single_next;
         }
     }
@@ -224,20 +237,24 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         if (lane == 0) atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT);
         // copies issued but not consumed may still be landing in this warp's ring:
         // give each a bounded chance before the CTA's shared memory is released
-        while (n_consumed < n_issued) {
-            (void)mbar_wait_bounded(&bars[n_consumed % NG], (n_consumed / NG) & 1u);
-            ++n_consumed;
+        while (in_flight > 0) {
+            (void)mbar_wait_bounded(&bars[s_cons], cons_parity);
+            --in_flight;
+            if (++s_cons == NG) {
+                s_cons = 0;
+                cons_parity ^= 1u;
+            }
         }
     }
 }
 
-template <int C>
-cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                          const float *W, const float *H, float *P, int64_t nnz, int sm_count,
-                          unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
+template <int C, bool HAS_PERM, bool HAS_SVAL>
+cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
+                           const float *W, const float *H, float *P, int64_t nnz, int sm_count,
+                           unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
-    const size_t smem = (size_t)RING_WARPS * RING_NG * RING_GROUP_BYTES + (size_t)RING_WARPS * RING_NG * 8;
-    auto kern = sddmm_ring_kernel<C>;
+    const size_t smem = (size_t)RING_WARPS * RING_NG * RingShape<C>::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
+    auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
@@ -245,6 +262,22 @@ cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_
     kern<<<(unsigned)sm_count, RING_WARPS * 32, smem, stream>>>(rows, cols, perm, sval, W, H, P, nnz, work_counter,
                                                                 dev_status);
     return cudaGetLastError();
+}
+
+template <int C>
+cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
+                          const float *W, const float *H, float *P, int64_t nnz, int sm_count,
+                          unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
+{
+#define RING_GO(PERM, SVAL) \
+    return launch_ring_tt<C, PERM, SVAL>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream)
+    if (perm) {
+        if (sval) RING_GO(true, true);
+        RING_GO(true, false);
+    }
+    if (sval) RING_GO(false, true);
+    RING_GO(false, false);
+#undef RING_GO
 }
 
 }  // namespace
