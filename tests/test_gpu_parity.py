@@ -243,3 +243,77 @@ def test_linearity_at_scale(engine):
         plan.execute(p["W"], p["H"], P4, None, flag)
         assert float((P1 - P4).abs().max()) <= 1e-5 * float(scale)
     plan.close()
+
+
+# ---- binning pass vs the reference's host tiling (bit-exact) ------------------
+
+TILING_KEYS = ("rows", "cols", "tiled_ind", "lastIdx_tile", "lastIdx_block_tile", "active_row", "n_actv_row")
+
+
+def _check_tiling(engine, M, N, rows, cols, pairs, expected=None):
+    plan = engine.plan_coo(M, N, rows, cols, 8)
+    for i, (pr, ct) in enumerate(pairs):
+        got = plan.export_tiling(int(pr), int(ct))
+        want = expected(i) if expected else oracle.cpu.rewrite_matrix_1d(rows, cols, None, M, N, int(pr), int(ct))
+        for k in TILING_KEYS:
+            assert np.array_equal(got[k], np.asarray(want[k])), (pr, ct, k)
+        assert got["max_active_row"] == int(want["max_active_row"]), (pr, ct)
+    plan.close()
+
+
+def test_export_tiling_matches_reference_golden(engine):
+    # the fixture holds what the reference's own make_CSR + rewrite_matrix_1D produced
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiling.npz"))
+    M, N = int(g["M"]), int(g["N"])
+    _check_tiling(engine, M, N, g["rows"], g["cols"], g["pairs"],
+                  expected=lambda i: {k: g[f"t{i}_{k}"] for k in TILING_KEYS + ("max_active_row",)})
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_export_tiling_matches_oracle(engine, seed):
+    rng = np.random.default_rng(seed)
+    M, N = 517, 300
+    rows, cols = random_coo(rng, M, N, 7001, empty_rows=[0, 3, 4, 100, 516] if seed else ())
+    pairs = [(32, 4096), (16, 64), (7, 33), (192, 50000), (1, 1), (5, 300), (64, 100), (517, 299)]
+    _check_tiling(engine, M, N, rows, cols, pairs)
+
+
+def test_export_tiling_config1_and_2_shapes(engine):
+    # the CLI pairs of the first two benchmark configurations: a single column tile, identity order
+    p = synth.to_numpy(synth.uniform_sparse(device="cpu"))
+    _check_tiling(engine, p["M"], p["N"], p["rows"], p["cols"], [(32, 4096)])
+    p = synth.to_numpy(synth.bag_of_words(device="cpu"))
+    _check_tiling(engine, p["M"], p["N"], p["rows"], p["cols"], [(192, 50000), (96, 50000), (24, 500)])
+
+
+# ---- the drop-in command line -------------------------------------------------
+
+def test_cli_prints_reference_lines_and_matches_oracle(tmp_path):
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "sddmm_gpu_b200", "csrc", "sddmm")
+    rng = np.random.default_rng(3)
+    M, N, K = 200, 150, 32
+    rows, cols = random_coo(rng, M, N, 3000)
+    vals = rng.integers(1, 20, rows.shape[0]).astype(np.float32)
+    mtx = str(tmp_path / "in.mtx")
+    api.mtx_write(mtx, M, N, rows, cols, vals)
+    out = str(tmp_path / "p.bin")
+    for extra, sv in (([], vals), (["--no-scale-by-s"], None)):
+        res = subprocess.run([exe, mtx, str(K), "192", "50000", "--dump-p", out, "--json", str(tmp_path / "r.json")] + extra,
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+        lines = [l for l in res.stdout.splitlines() if l.strip()]
+        assert lines[0] == f"Matrix info:  rows: {M}, cols: {N}, nnz: {rows.shape[0]}"
+        assert lines[1].startswith("Tilesize: X = 50000, tilesize: Y = 192, TB: ")
+        assert lines[2].startswith(f"Time for SDDMM with K = {K} : ") and lines[2].endswith(" ms")
+        W = oracle.cpu.initial(M, K)     # the reference's operand initialisation
+        H = oracle.cpu.initial(N, K)
+        assert_parity(np.fromfile(out, np.float32), rows, cols, W, H, sv)
+    # errors: non-zero exit code and one line on stderr instead of an assert
+    bad = subprocess.run([exe, str(tmp_path / "missing.mtx"), "32", "192", "50000"], capture_output=True, text=True)
+    assert bad.returncode != 0 and bad.stderr.startswith("sddmm: ")
+    bad = subprocess.run([exe, mtx, "30", "192", "50000"], capture_output=True, text=True)
+    assert bad.returncode != 0 and "K must be" in bad.stderr
