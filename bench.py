@@ -149,13 +149,17 @@ def hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def ncu_traffic(workload):
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (keyed by workload and kernel; full-size captures, 1-pass metrics)
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    ("c4_rmat_scale22_ef24_K256", "ring"): 55_959_587_072 + 392_071_680,   # profiles/sddmm_ring_kernel_c4_rmat_scale22_K256.md
+    ("c4_rmat_scale22_ef24_K256", "panel"): 56_620_000_000 + 697_190_000,  # profiles/sddmm_panel_and_gather_kernels_rmat_K256.md
+}
+
+
+def ncu_traffic(workload, kernel):
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
-    try:
-        t = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
-        return t.get(workload)
-    except Exception:
-        return None
+    return NCU_DRAM_BYTES_PER_LAUNCH.get((workload, kernel))
 
 
 def sample_blocks(nnz, n_sample, n_blocks=64):
@@ -345,7 +349,7 @@ def main():
     alg_bytes = synth.algorithmic_bytes(shard.n_rows, b - a, K, m_nz_local, n_nz_local)
     kernel_ms = statistics.mean(step_ms)
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic = ncu_traffic(p["workload"]) if world == 1 else None
+    traffic = ncu_traffic(p["workload"], kernel_name) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": alg_bytes,
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(step_ms),

@@ -69,9 +69,17 @@ def gather_p(P_local, shard, group=None):
     if not dist.is_initialized() or shard.world == 1:
         return P_local
     sizes = [int(shard.nnz_cuts[g + 1] - shard.nnz_cuts[g]) for g in range(shard.world)]
-    out = [torch.empty(s, dtype=P_local.dtype, device=P_local.device) for s in sizes]
-    dist.all_gather(out, P_local, group=group)
-    return torch.cat(out)
+    # the shards differ in length, so every rank broadcasts its own slice
+    out = torch.empty(sum(sizes), dtype=P_local.dtype, device=P_local.device)
+    off = 0
+    for g, n in enumerate(sizes):
+        piece = out[off:off + n]
+        if g == shard.rank:
+            piece.copy_(P_local)
+        if n > 0:
+            dist.broadcast(piece, src=g, group=group)
+        off += n
+    return out
 
 
 class ShardedSddmm:
