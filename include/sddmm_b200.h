@@ -154,6 +154,38 @@ SDDMM_API int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info);
  * computed on the device on request and cached in the plan. */
 SDDMM_API int sddmm_plan_count_cols(sddmm_plan_t p, int64_t *n_nonempty_cols);
 
+/*
+ * The same count for callers that may not allocate device memory (no
+ * counterpart in the reference: it allocates and frees on every call).
+ *
+ * Meant for hosts that cannot enter the CUDA allocator: a process whose
+ * framework already owns all device memory, a loop that cannot take the
+ * device-wide synchronisation cudaMalloc/cudaFree imply, a plug-in running
+ * inside another library's callback.  This entry point calls no cudaMalloc,
+ * cudaFree or other allocating routine and needs no handle or plan: its scratch
+ * (one mark per column plus a counter) is a fixed array inside the library image,
+ * SDDMM_NOALLOC_SCRATCH_BYTES per GPU that loads the library, held until exit.
+ *
+ *   device   : CUDA device that owns d_cols; made current by the call.
+ *   d_cols   : nnz column indices in device memory (any order); indices outside
+ *              [0, N) are ignored.
+ *   N        : number of columns; N > SDDMM_NOALLOC_MAX_COLS is rejected with
+ *              SDDMM_INVALID_ARG and a message in errbuf (use
+ *              sddmm_plan_count_cols for larger matrices).
+ *   cuda_stream : cudaStream_t to run on (NULL = the default stream); the call
+ *              returns after the count has been copied back.
+ * The first call on each device also looks up the scratch array's device address;
+ * make that first call outside any stream capture.  All calls on a device share
+ * the scratch, which keeps the previous call's contents: every call clears what
+ * it uses before it starts, and calls that overlap on one GPU (two streams or two
+ * threads at once) race with each other -- serialise them.
+ */
+#define SDDMM_NOALLOC_MAX_COLS (8 * 1024 * 1024)
+#define SDDMM_NOALLOC_SCRATCH_BYTES (SDDMM_NOALLOC_MAX_COLS + 256)
+SDDMM_API int sddmm_count_cols_noalloc(int device, const int32_t *d_cols, int64_t nnz, int64_t N,
+                                       void *cuda_stream, int64_t *n_nonempty_cols, char *errbuf,
+                                       int errbuf_len);
+
 /* Row pointer over all M rows (M + 1 int64 entries, host buffer), the GPU
  * replacement of make_CSR's row_ptr/row_holder pair (util.h:131-153). */
 SDDMM_API int sddmm_plan_export_row_ptr(sddmm_plan_t p, int64_t *row_ptr);

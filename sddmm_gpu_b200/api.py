@@ -29,7 +29,7 @@ PLAN_DEVICE_INDICES = 0x2
 EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_coo",
-    "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_plan_export_row_ptr",
+    "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
@@ -77,6 +77,7 @@ def lib():
     L.sddmm_coo.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, vp]
     L.sddmm_plan_get_info.argtypes = [vp, C.POINTER(PlanInfo)]
     L.sddmm_plan_count_cols.argtypes = [vp, C.POINTER(i64)]
+    L.sddmm_count_cols_noalloc.argtypes = [C.c_int, vp, i64, i64, vp, C.POINTER(i64), C.c_char_p, C.c_int]
     L.sddmm_plan_export_row_ptr.argtypes = [vp, vp]
     L.sddmm_plan_export_tiling.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, vp, vp, vp, vp, C.POINTER(i32)]
     L.sddmm_partition_rows.argtypes = [i64, i64, vp, C.c_int, C.c_int, vp, vp]
@@ -231,6 +232,24 @@ class Plan:
         out["ntile_c"] = ntile_c
         out["max_active_block"] = max_blk
         return out
+
+
+NOALLOC_MAX_COLS = 8 * 1024 * 1024
+
+
+def count_cols_noalloc(d_cols, N, device=0, cuda_stream=None, nnz=None):
+    """Distinct columns among the device-resident column indices `d_cols`, computed
+    without any device allocation (sddmm_count_cols_noalloc).  For callers that are
+    not allowed to enter the CUDA allocator; N is limited to NOALLOC_MAX_COLS by the
+    library's built-in scratch.  Calls on one GPU must not overlap."""
+    if nnz is None:
+        nnz = int(d_cols.shape[0])
+    out = C.c_int64()
+    err = C.create_string_buffer(256)
+    st = lib().sddmm_count_cols_noalloc(device, _ptr(d_cols), nnz, N, cuda_stream, C.byref(out), err, 256)
+    if st != OK:
+        raise SddmmError(st, err.value.decode())
+    return out.value
 
 
 # ---- host-only helpers (no GPU needed) -------------------------------------
