@@ -374,6 +374,73 @@ cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, i
 
 
 // ---------------------------------------------------------------------------
+// Hub-column hints for the ring kernel
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int DEG_CAP = 1 << 16;  // degrees are histogrammed exactly up to here
+
+__global__ void col_degree_kernel(const int32_t *__restrict__ cols, int64_t nnz, int32_t *deg)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x)
+        atomicAdd(&deg[cols[i]], 1);
+}
+__global__ void degree_histogram_kernel(const int32_t *__restrict__ deg, int64_t N, unsigned long long *hist)
+{
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < N; c += (int64_t)gridDim.x * blockDim.x) {
+        const int d = deg[c];
+        if (d > 0) atomicAdd(&hist[d < DEG_CAP ? d : DEG_CAP - 1], 1ull);
+    }
+}
+__global__ void flag_cols_kernel(const int32_t *__restrict__ cols, const int32_t *__restrict__ deg, int64_t nnz,
+                                 int threshold, int32_t *cols_out)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t c = cols[i];
+        cols_out[i] = deg[c] >= threshold ? (int32_t)((uint32_t)c | 0x80000000u) : c;
+    }
+}
+
+}  // namespace
+
+cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t N, int64_t row_bytes,
+                                   int64_t budget_bytes, int32_t *d_cols_hinted, int64_t *n_hub_cols,
+                                   int *degree_threshold, cudaStream_t stream)
+{
+    *n_hub_cols = 0;
+    *degree_threshold = 0;
+    if (nnz == 0 || N == 0) return cudaSuccess;
+    Scratch deg, hist;
+    CK(deg.reserve(sizeof(int32_t) * (size_t)N));
+    CK(hist.reserve(sizeof(unsigned long long) * DEG_CAP));
+    CK(cudaMemsetAsync(deg.ptr, 0, sizeof(int32_t) * (size_t)N, stream));
+    CK(cudaMemsetAsync(hist.ptr, 0, sizeof(unsigned long long) * DEG_CAP, stream));
+    col_degree_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols_p, nnz, (int32_t *)deg.ptr);
+    degree_histogram_kernel<<<grid_for(N), TPB, 0, stream>>>((const int32_t *)deg.ptr, N, (unsigned long long *)hist.ptr);
+    CK(cudaGetLastError());
+    std::vector<unsigned long long> h(DEG_CAP);
+    CK(cudaMemcpyAsync(h.data(), hist.ptr, sizeof(unsigned long long) * DEG_CAP, cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    // the most popular columns first, until their rows of H fill the budget; a
+    // column used once gains nothing from staying in L2
+    const int64_t max_cols = budget_bytes / row_bytes;
+    int64_t taken = 0;
+    int t = DEG_CAP;
+    for (int d = DEG_CAP - 1; d >= 2; --d) {
+        if (taken + (int64_t)h[d] > max_cols) break;
+        taken += (int64_t)h[d];
+        t = d;
+    }
+    if (t == DEG_CAP) t = INT32_MAX;  // nothing fits: no column is marked
+    flag_cols_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols_p, (const int32_t *)deg.ptr, nnz, t, d_cols_hinted);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(stream));
+    *n_hub_cols = taken;
+    *degree_threshold = t;
+    return cudaSuccess;
+}
+
+// ---------------------------------------------------------------------------
 // Reference-layout tiling tables (test hook)
 // ---------------------------------------------------------------------------
 namespace {

@@ -52,6 +52,13 @@ cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, i
                              int64_t *n_items, int32_t **d_item_rows, int64_t *n_item_rows,
                              cudaStream_t stream);
 
+// Hub-column hints for the ring kernel: d_cols_hinted[j] = d_cols_p[j] with bit 31
+// set when the column is among the most popular ones whose rows of H together fit
+// budget_bytes (chosen by exact column degree, most popular first).
+cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t N, int64_t row_bytes,
+                                   int64_t budget_bytes, int32_t *d_cols_hinted, int64_t *n_hub_cols,
+                                   int *degree_threshold, cudaStream_t stream);
+
 // Reference-layout tiling tables (test hook); see sddmm_plan_export_tiling.
 struct TilingTables {
     int32_t *t_rows, *t_cols, *tiled_ind, *lastIdx_tile, *lastIdx_block_tile, *active_row, *n_actv_row;

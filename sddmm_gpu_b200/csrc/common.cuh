@@ -58,8 +58,9 @@ cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *
 // shared-memory rings, work handed out dynamically through *work_counter (one
 // device word, zeroed by the launcher).  K must satisfy ring_supports(K).
 bool ring_supports(int K);
+// cols_hinted: bit 31 of every column index marks a hub column (see build_hub_column_hints).
 cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                        const float *W, const float *H, float *P, int64_t nnz, int K, int sm_count,
+                        const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
 
 // One-time per-process kernel attribute set-up (opt-in shared memory sizes).

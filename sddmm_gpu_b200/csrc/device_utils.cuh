@@ -90,11 +90,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out.
+// Bounded wait: false when the limit ran out.  Polls back off with a short
+// sleep so that a waiting warp does not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, unsigned parity)
 {
-    for (int it = 0; it < MBAR_SPIN_LIMIT; ++it)
+    for (int it = 0; it < MBAR_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(it < 16 ? 32 : 256);
+    }
     return false;
 }
 // 1-D bulk asynchronous copy global -> shared, completion counted in bytes on
@@ -106,6 +109,28 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
             smem_u32(dst_smem)),
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
+}
+// The same copy with an L2 eviction-priority hint (a createpolicy descriptor).
+__device__ __forceinline__ void bulk_g2s_hint(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar,
+                                              uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 
 // ---------------------------------------------------------------------------

@@ -7,6 +7,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -46,6 +47,8 @@ struct sddmm_plan_s {
     WorkItem *d_items = nullptr;
     int64_t n_items = 0;
     int32_t *d_item_rows = nullptr;  // distinct rows of every item, concatenated
+    int32_t *d_cols_hint = nullptr;  // processing-order columns with hub marks (ring kernel), or null
+    int64_t n_hub_cols = 0;
     int64_t n_item_rows = 0;
     int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
     // staging for host operands (allocated on first use)
@@ -110,6 +113,7 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_row_ptr);
     cudaFree(p->d_items);
     cudaFree(p->d_item_rows);
+    cudaFree(p->d_cols_hint);
     cudaFree(p->d_W);
     cudaFree(p->d_H);
     cudaFree(p->d_S);
@@ -314,6 +318,19 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
     PLAN_TRY(build_work_items(rows_p, cols_p, nnz, p->cfg.panel_rows, p->col_tile, p->cfg.item_nnz, &p->d_items,
                               &p->n_items, &p->d_item_rows, &p->n_item_rows, s));
     p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items + sizeof(int32_t) * (size_t)p->n_item_rows);
+    // Hub-column marks for the ring kernel, when H is too large to live in L2 as a
+    // whole.  SDDMM_L2_HUB_MB overrides the share of L2 set aside for hub rows (0 = off).
+    if (ring_supports(K) && nnz > 0) {
+        int64_t budget_mb = 48;
+        if (const char *env = std::getenv("SDDMM_L2_HUB_MB")) budget_mb = std::atoll(env);
+        const int64_t row_bytes = (int64_t)K * 4;
+        if (budget_mb > 0 && N * row_bytes > budget_mb * (1ll << 20)) {
+            PLAN_TRY(dev_alloc(p, &p->d_cols_hint, (size_t)nnz));
+            int thr = 0;
+            PLAN_TRY(build_hub_column_hints(cols_p, nnz, N, row_bytes, budget_mb * (1ll << 20), p->d_cols_hint,
+                                            &p->n_hub_cols, &thr, s));
+        }
+    }
     PLAN_TRY(cudaEventRecord(t1, s));
     PLAN_TRY(cudaEventSynchronize(t1));
     PLAN_TRY(cudaEventElapsedTime(&p->plan_ms, t0, t1));
@@ -402,8 +419,8 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             return SDDMM_INVALID_ARG;
         }
         if (use_ring)
-            CUDA_TRY(h, launch_ring(rows_p, cols_p, perm, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, h->d_work_counter,
-                                    h->d_status, s));
+            CUDA_TRY(h, launch_ring(rows_p, p->d_cols_hint ? p->d_cols_hint : cols_p, perm, dS, dW, dH, dP, p->nnz, p->K,
+                                    p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status, s));
         else
             CUDA_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K,
                                      p->cfg, h->sm_count, h->d_status, s));

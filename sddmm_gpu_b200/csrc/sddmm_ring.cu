@@ -60,7 +60,7 @@ struct RingShape {
     static_assert(B >= 1 && B <= 32, "group size");
 };
 
-template <int C, bool HAS_PERM, bool HAS_SVAL>
+template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT>
 __global__ void __launch_bounds__(RING_WARPS * 32, 1)
 sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
                   const int32_t *__restrict__ perm, const float *__restrict__ sval,
@@ -96,6 +96,14 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     bool timed_out = false;
     float4 wc[C];  // W row of a single-row group
     int wc_row = -1;
+    // HAS_HINT: bit 31 of a column index marks a hub column (chosen by the plan so
+    // that all hub rows of H fit a share of L2); its copy asks L2 to keep the row,
+    // every other copy asks L2 to drop the row first.
+    uint64_t pol_keep = 0, pol_drop = 0;
+    if (HAS_HINT) {
+        pol_keep = l2_policy_evict_last();
+        pol_drop = l2_policy_evict_first();
+    }
 
     // One lane arms the slot's mbarrier with the byte count and issues the B row
     // copies (column indices arrive by shuffle, so the issuing code is uniform).
@@ -111,8 +119,15 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
                          "r"((unsigned)(B * R::ROW_BYTES))
                          : "memory");
 #pragma unroll
-            for (int j = 0; j < B; ++j)
-                bulk_g2s(slot + j * R::ROW_BYTES, Hb + (size_t)cj[j] * R::ROW_BYTES, R::ROW_BYTES, bar);
+            for (int j = 0; j < B; ++j) {
+                if (HAS_HINT) {
+                    const unsigned col = cj[j] & 0x7fffffffu;
+                    bulk_g2s_hint(slot + j * R::ROW_BYTES, Hb + (size_t)col * R::ROW_BYTES, R::ROW_BYTES, bar,
+                                  (cj[j] >> 31) ? pol_keep : pol_drop);
+                } else {
+                    bulk_g2s(slot + j * R::ROW_BYTES, Hb + (size_t)cj[j] * R::ROW_BYTES, R::ROW_BYTES, bar);
+                }
+            }
         }
         s_issue = (s_issue + 1 == NG) ? 0 : s_issue + 1;
         ++in_flight;
@@ -142,6 +157,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
                 if (lane < tail) {
                     r = __ldcs(rows + off + lane);
                     c = __ldcs(cols + off + lane);
+                    if (HAS_HINT) c &= 0x7fffffff;
                 }
                 const float res = warp_step<32, C, B, false>(W, H, r, c, tail, K4, lane);
                 if (lane < tail) store(off + lane, res);
@@ -248,13 +264,13 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     }
 }
 
-template <int C, bool HAS_PERM, bool HAS_SVAL>
+template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT>
 cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                            const float *W, const float *H, float *P, int64_t nnz, int sm_count,
                            unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
     const size_t smem = (size_t)RING_WARPS * RING_NG * RingShape<C>::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
-    auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL>;
+    auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL, HAS_HINT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
@@ -266,17 +282,24 @@ cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32
 
 template <int C>
 cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                          const float *W, const float *H, float *P, int64_t nnz, int sm_count,
+                          const float *W, const float *H, float *P, int64_t nnz, bool cols_hinted, int sm_count,
                           unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
-#define RING_GO(PERM, SVAL) \
-    return launch_ring_tt<C, PERM, SVAL>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream)
+#define RING_GO(PERM, SVAL, HINT)                                                                                   \
+    return launch_ring_tt<C, PERM, SVAL, HINT>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, \
+                                               stream)
+#define RING_GO2(PERM, SVAL)              \
+    do {                                  \
+        if (cols_hinted) RING_GO(PERM, SVAL, true); \
+        RING_GO(PERM, SVAL, false);       \
+    } while (0)
     if (perm) {
-        if (sval) RING_GO(true, true);
-        RING_GO(true, false);
+        if (sval) RING_GO2(true, true);
+        RING_GO2(true, false);
     }
-    if (sval) RING_GO(false, true);
-    RING_GO(false, false);
+    if (sval) RING_GO2(false, true);
+    RING_GO2(false, false);
+#undef RING_GO2
 #undef RING_GO
 }
 
@@ -285,15 +308,15 @@ cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_
 bool ring_supports(int K) { return K == 128 || K == 256 || K == 512 || K == 1024; }
 
 cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                        const float *W, const float *H, float *P, int64_t nnz, int K, int sm_count,
+                        const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
     if (nnz == 0) return cudaSuccess;
     switch (K) {
-    case 128: return launch_ring_t<1>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream);
-    case 256: return launch_ring_t<2>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream);
-    case 512: return launch_ring_t<4>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream);
-    case 1024: return launch_ring_t<8>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, stream);
+    case 128: return launch_ring_t<1>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 256: return launch_ring_t<2>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 512: return launch_ring_t<4>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 1024: return launch_ring_t<8>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     default: return cudaErrorInvalidValue;
     }
 }
