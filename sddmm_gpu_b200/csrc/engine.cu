@@ -40,7 +40,7 @@ struct sddmm_plan_s {
     PanelConfig cfg{};
     // pattern, input order
     int32_t *d_rows = nullptr, *d_cols = nullptr;
-    bool owns_indices = true;
+    bool owns_rows = true, owns_cols = true;
     // pattern, tiled order (only when n_col_tiles > 1)
     int32_t *d_rows_t = nullptr, *d_cols_t = nullptr, *d_perm = nullptr;
     int64_t *d_row_ptr = nullptr;
@@ -103,10 +103,8 @@ cudaError_t dev_alloc(sddmm_plan_s *p, T **ptr, size_t count)
 
 void free_plan_memory(sddmm_plan_s *p)
 {
-    if (p->owns_indices) {
-        cudaFree(p->d_rows);
-        cudaFree(p->d_cols);
-    }
+    if (p->owns_rows) cudaFree(p->d_rows);
+    if (p->owns_cols) cudaFree(p->d_cols);
     cudaFree(p->d_rows_t);
     cudaFree(p->d_cols_t);
     cudaFree(p->d_perm);
@@ -257,8 +255,15 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
     const bool dev_idx = (flags & SDDMM_PLAN_DEVICE_INDICES) != 0;
     if (dev_idx) {
         p->d_rows = const_cast<int32_t *>(rows);
-        p->d_cols = const_cast<int32_t *>(cols);
-        p->owns_indices = false;
+        p->owns_rows = false;
+        if (((uintptr_t)cols & 15u) == 0) {
+            p->d_cols = const_cast<int32_t *>(cols);
+            p->owns_cols = false;
+        } else {
+            // the kernels read column indices with 16-byte vector loads: realign a borrowed array
+            PLAN_TRY(dev_alloc(p, &p->d_cols, (size_t)nnz));
+            if (nnz > 0) PLAN_TRY(cudaMemcpyAsync(p->d_cols, cols, sizeof(int32_t) * nnz, cudaMemcpyDeviceToDevice, s));
+        }
     } else {
         PLAN_TRY(dev_alloc(p, &p->d_rows, (size_t)nnz));
         PLAN_TRY(dev_alloc(p, &p->d_cols, (size_t)nnz));

@@ -7,23 +7,25 @@
 // rate.  Gathering into registers caps the bytes in flight at a fraction of the
 // register file.  Here every H row is one cp.async.bulk of K*4 bytes into a
 // shared-memory slot, completion counted on an mbarrier, so an SM keeps
-// NWARPS * (NG-1) * 4 KB (~128 KB) of gathers in flight without holding a single
+// NWARPS * (NG-1) * 4 KB (~100 KB) of gathers in flight without holding a single
 // register for them, and the address arithmetic per 16 bytes disappears.
 //
 // Shape.  One persistent CTA per SM, NWARPS independent warps, no CTA-wide
 // synchronisation after set-up.  A warp owns NG ring slots of one group each; a
 // group is B = 4096 / (K*4) consecutive nonzeros (4 KB of H rows).  Work is
-// handed out in blocks of BLOCK_GROUPS groups through a global counter
-// (atomicAdd), in nonzero order, so concurrently running warps work on
-// neighbouring rows of S.  Per group: lane t < B issues the copy of H[col_t],
-// lane 0 arms the slot's mbarrier with the byte count; NG-1 groups later the
-// warp waits on that mbarrier (bounded), reads the rows back with 128-bit
-// shared-memory loads and multiplies with W.
+// handed out in blocks of groups through a global counter (atomicAdd), in
+// nonzero order, so concurrently running warps work on neighbouring rows of S.
+// Per group: one lane arms the slot's mbarrier with the byte count and issues
+// the B row copies; NG-1 groups later the warp waits on that mbarrier (bounded).
+// The 32 lanes are B sets of 32/B lanes, one set per nonzero: every lane reads 8
+// float4 of its nonzero's H row from shared memory, multiplies with its share of
+// the W row, and the sets finish their dot products together with log2(32/B)
+// __shfl_xor_sync steps.
 //
-// W.  Consecutive groups of a warp mostly lie in one row of S, whose W row lives
-// in registers and is reloaded only when the row changes; groups that straddle
-// rows load one W row per nonzero.  Both are fetched from global memory (L1/L2)
-// one group ahead, right after the previous group's FMAs.
+// W.  Consecutive nonzeros handled by a lane set mostly lie in one row of S, so
+// a lane keeps its share of that W row in registers and reloads it (from global
+// memory, L1/L2) only when the row changes -- one group ahead, right after the
+// previous group's FMAs.
 //
 // Supported: K = 128 * C with C in {1, 2, 4, 8} (K = 128 ... 1024).
 #include <cuda_runtime.h>
@@ -44,36 +46,69 @@ namespace {
 #ifndef SDDMM_RING_NG
 #define SDDMM_RING_NG 2
 #endif
-#ifndef SDDMM_RING_GROUP_BYTES
-#define SDDMM_RING_GROUP_BYTES 4096
-#endif
 constexpr int RING_WARPS = SDDMM_RING_WARPS;
 constexpr int RING_NG = SDDMM_RING_NG;  // ring slots (groups) per warp
-constexpr int RING_GROUP_BYTES = SDDMM_RING_GROUP_BYTES;
-constexpr int RING_BLOCK_GROUPS = 128;  // groups per dynamically scheduled block
+constexpr int RING_GROUP_BYTES = 4096;  // H bytes of one group
 
+// Geometry for K = 128 * C floats per row.  A group is B rows of H (4 KB); the
+// 32 lanes split into B sets of LPN lanes, one set per nonzero, and every lane
+// handles F = 8 float4 of its nonzero's row, interleaved with the other lanes of
+// its set (lane l takes float4 c*LPN + l), so that a 128-bit shared-memory load
+// of a set covers LPN*16 consecutive bytes and the dot product is finished with
+// log2(LPN) shuffles -- all B nonzeros of the group reduce at the same time.
 template <int C>
 struct RingShape {
     static constexpr int ROW_BYTES = C * 512;
-    static constexpr int SLOT_BYTES = RING_GROUP_BYTES > ROW_BYTES ? RING_GROUP_BYTES : ROW_BYTES;
-    static constexpr int B = SLOT_BYTES / ROW_BYTES;  // nonzeros per group
-    static_assert(B >= 1 && B <= 32, "group size");
+    static constexpr int B = RING_GROUP_BYTES > ROW_BYTES ? RING_GROUP_BYTES / ROW_BYTES : 1;
+    static constexpr int LPN = 32 / B;                   // lanes per nonzero
+    static constexpr int F = ROW_BYTES / 16 / LPN;       // float4 per lane per row
+    // with 4 lanes per row two rows share a quarter-warp: pad the row stride so
+    // that their 64-byte pieces fall into different banks
+    static constexpr int ROW_STRIDE = ROW_BYTES + (LPN == 4 ? 64 : 0);
+    static constexpr int SLOT_BYTES = (B * ROW_STRIDE + 127) / 128 * 128;
+    static_assert(B >= 1 && B <= 8 && LPN * B == 32, "group geometry");
 };
+
+// B consecutive column indices, loaded as one vector by every lane (same
+// address for the whole warp).  p is aligned to min(16, 4*B) bytes.
+template <int B>
+struct ColVec {
+    int v[B];
+};
+template <int B>
+__device__ __forceinline__ ColVec<B> load_cols(const int32_t *p)
+{
+    ColVec<B> r;
+    if constexpr (B == 1) {
+        r.v[0] = __ldcs(p);
+    } else if constexpr (B == 2) {
+        const int2 t = __ldcs(reinterpret_cast<const int2 *>(p));
+        r.v[0] = t.x; r.v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < B / 4; ++i) {
+            const int4 t = __ldcs(reinterpret_cast<const int4 *>(p) + i);
+            r.v[4 * i] = t.x; r.v[4 * i + 1] = t.y; r.v[4 * i + 2] = t.z; r.v[4 * i + 3] = t.w;
+        }
+    }
+    return r;
+}
 
 template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT>
 __global__ void __launch_bounds__(RING_WARPS * 32, 1)
 sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
                   const int32_t *__restrict__ perm, const float *__restrict__ sval,
                   const float *__restrict__ W, const float *__restrict__ H, float *__restrict__ P,
-                  int64_t nnz, unsigned long long *work_counter, int *dev_status)
+                  int64_t nnz, int block_groups, unsigned long long *work_counter, int *dev_status)
 {
     using R = RingShape<C>;
-    constexpr int B = R::B;
-    constexpr int NG = RING_NG;
+    constexpr int B = R::B, LPN = R::LPN, F = R::F, NG = RING_NG;
     constexpr int K4 = 32 * C;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    const int g = lane / LPN;  // which nonzero of a group this lane works on
+    const int l = lane % LPN;  // position inside the lane set
     // per warp: NG slots of one group each, then (after all rings) NG mbarriers per warp
     unsigned char *ring = smem_raw + (size_t)warp * NG * R::SLOT_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)RING_WARPS * NG * R::SLOT_BYTES) + warp * NG;
@@ -82,10 +117,9 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     __syncwarp();
 
     const int64_t n_groups = nnz / B;  // full groups; the remainder is handled at the end
-    const int64_t n_blocks = (n_groups + RING_BLOCK_GROUPS - 1) / RING_BLOCK_GROUPS;
+    const int64_t n_blocks = (n_groups + block_groups - 1) / block_groups;
     const char *Hb = reinterpret_cast<const char *>(H);
-    const char *W_lane = reinterpret_cast<const char *>(W) + lane * 16;
-    const int il = lane & (B - 1);  // lanes >= B mirror a valid nonzero of the group
+    const char *W_lane = reinterpret_cast<const char *>(W) + l * 16;
 
     // Ring bookkeeping.  Issue and consume each walk the NG slots round-robin; a
     // slot's mbarrier phase flips every time the slot is reused, so the parity to
@@ -94,8 +128,8 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     unsigned cons_parity = 0;          // parity of the consumer's current walk
     unsigned in_flight = 0;            // groups issued and not yet consumed
     bool timed_out = false;
-    float4 wc[C];  // W row of a single-row group
-    int wc_row = -1;
+    float4 wc[F];     // this lane's share of the W row of its lane set's current row of S
+    int wc_row = -1;  // that row (-1: none)
     // HAS_HINT: bit 31 of a column index marks a hub column (chosen by the plan so
     // that all hub rows of H fit a share of L2); its copy asks L2 to keep the row,
     // every other copy asks L2 to drop the row first.
@@ -105,27 +139,23 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         pol_drop = l2_policy_evict_first();
     }
 
-    // One lane arms the slot's mbarrier with the byte count and issues the B row
-    // copies (column indices arrive by shuffle, so the issuing code is uniform).
-    auto issue = [&](int c_mine) {
-        unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
-        uint64_t *bar = &bars[s_issue];
-        unsigned cj[B];
-#pragma unroll
-        for (int j = 0; j < B; ++j) cj[j] = (unsigned)__shfl_sync(FULL, c_mine, j);
+    // One lane arms the slot's mbarrier with the byte count and issues the B row copies.
+    auto issue = [&](const ColVec<B> &cv) {
         if (lane == 0) {
+            unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
+            uint64_t *bar = &bars[s_issue];
             asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(
                              smem_u32(bar)),
                          "r"((unsigned)(B * R::ROW_BYTES))
                          : "memory");
 #pragma unroll
             for (int j = 0; j < B; ++j) {
+                const unsigned cj = (unsigned)cv.v[j];
                 if (HAS_HINT) {
-                    const unsigned col = cj[j] & 0x7fffffffu;
-                    bulk_g2s_hint(slot + j * R::ROW_BYTES, Hb + (size_t)col * R::ROW_BYTES, R::ROW_BYTES, bar,
-                                  (cj[j] >> 31) ? pol_keep : pol_drop);
+                    bulk_g2s_hint(slot + j * R::ROW_STRIDE, Hb + (size_t)(cj & 0x7fffffffu) * R::ROW_BYTES, R::ROW_BYTES,
+                                  bar, (cj >> 31) ? pol_keep : pol_drop);
                 } else {
-                    bulk_g2s(slot + j * R::ROW_BYTES, Hb + (size_t)cj[j] * R::ROW_BYTES, R::ROW_BYTES, bar);
+                    bulk_g2s(slot + j * R::ROW_STRIDE, Hb + (size_t)cj * R::ROW_BYTES, R::ROW_BYTES, bar);
                 }
             }
         }
@@ -141,6 +171,12 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
             if (HAS_SVAL) v *= __ldcs(sval + j);
             __stcs(P + j, v);
         }
+    };
+    auto load_w = [&](int r) {
+        const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)(unsigned)r * R::ROW_BYTES);
+#pragma unroll
+        for (int c = 0; c < F; ++c) wc[c] = __ldg(wrow + c * LPN);
+        wc_row = r;
     };
 
     while (!timed_out) {
@@ -164,89 +200,48 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
             }
             continue;
         }
-        const int64_t g0 = (int64_t)blk * RING_BLOCK_GROUPS;
-        const int n = (int)((n_groups - g0) < RING_BLOCK_GROUPS ? (n_groups - g0) : RING_BLOCK_GROUPS);
-        const int32_t *brow = rows + g0 * B + il;
-        const int32_t *bcol = cols + g0 * B + il;
+        const int64_t g0 = (int64_t)blk * block_groups;
+        const int n = (int)((n_groups - g0) < block_groups ? (n_groups - g0) : block_groups);
+        const int32_t *brow = rows + g0 * B + g;  // row of this lane set's nonzero in group q: brow[q * B]
+        const int32_t *bcol = cols + g0 * B;      // the B columns of group q start at bcol + q * B
+        auto clampq = [&](int q) { return q < n ? q : n - 1; };  // past the end the last group is re-read
 
-        // (row, col) of nonzero `il` of group q of this block; past the end the last group is re-read
-        auto load_idx = [&](int q, int &r, int &c) {
-            const int qq = q < n ? q : n - 1;
-            r = __ldcs(brow + qq * B);
-            c = __ldcs(bcol + qq * B);
-        };
-
-        // index registers of the groups ahead: r_q[i], c_q[i] belong to group (current + i)
-        int r_q[NG], c_q[NG];
-#pragma unroll
-        for (int i = 0; i < NG; ++i) load_idx(i, r_q[i], c_q[i]);
-        // prologue: NG-1 groups in flight
+        // prologue: NG-1 groups in flight, W of the first group, indices one step ahead
 #pragma unroll
         for (int i = 0; i < NG - 1; ++i)
-            if (i < n) issue(c_q[i]);
-
-        // W of the next group: a group whose nonzeros share one row keeps that row
-        // of W in registers (fetched here, one group ahead, only when the row
-        // changes); a group that straddles rows reads W per nonzero when consumed.
-        auto prefetch_w = [&](int r_mine) {
-            const int r0 = __shfl_sync(FULL, r_mine, 0);
-            const bool single = __all_sync(FULL, r_mine == r0);
-            if (single && r0 != wc_row) {
-                const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)(unsigned)r0 * R::ROW_BYTES);
-#pragma unroll
-                for (int c = 0; c < C; ++c) wc[c] = __ldg(wrow + c * 32);
-                wc_row = r0;
-            }
-            return single;
-        };
-        bool single = prefetch_w(r_q[0]);
+            if (i < n) issue(load_cols<B>(bcol + i * B));
+        ColVec<B> cv = load_cols<B>(bcol + clampq(NG - 1) * B);  // columns of group q + NG - 1
+        {
+            const int r0 = __ldcs(brow);
+            if (r0 != wc_row) load_w(r0);
+        }
+        int r_next = __ldcs(brow + clampq(1) * B);  // row of group q + 1
 
         for (int q = 0; q < n; ++q) {
             // keep NG-1 groups in flight: group q + NG - 1 goes into the slot freed by group q - 1
-            if (q + NG - 1 < n) issue(c_q[NG - 1]);
+            if (q + NG - 1 < n) issue(cv);
+            cv = load_cols<B>(bcol + clampq(q + NG) * B);
+            const int r_fut = __ldcs(brow + clampq(q + 2) * B);
             // wait for group q
             if (!mbar_try_wait(&bars[s_cons], cons_parity) && !mbar_wait_bounded(&bars[s_cons], cons_parity)) {
                 timed_out = true;
                 break;
             }
-            const float4 *slot = reinterpret_cast<const float4 *>(ring + s_cons * R::SLOT_BYTES) + lane;
+            const float4 *srow = reinterpret_cast<const float4 *>(ring + s_cons * R::SLOT_BYTES + g * R::ROW_STRIDE) + l;
             --in_flight;
             if (++s_cons == NG) {
                 s_cons = 0;
                 cons_parity ^= 1u;
             }
-            float acc[B];
-            if (single) {
+            float acc = 0.f;
 #pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    acc[j] = 0.f;
+            for (int c = 0; c < F; ++c) acc = dot4(wc[c], srow[c * LPN], acc);
+            // W of the next group, fetched while this group is reduced and stored
+            if (r_next != wc_row) load_w(r_next);
+            r_next = r_fut;
 #pragma unroll
-                    for (int c = 0; c < C; ++c) acc[j] = dot4(wc[c], slot[j * K4 + c * 32], acc[j]);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    acc[j] = 0.f;
-                    const unsigned rj = (unsigned)__shfl_sync(FULL, r_q[0], j);
-                    const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)rj * R::ROW_BYTES);
-#pragma unroll
-                    for (int c = 0; c < C; ++c) acc[j] = dot4(__ldg(wrow + c * 32), slot[j * K4 + c * 32], acc[j]);
-                }
-            }
-            // shift the index queue, fetch the indices of group q + NG, prefetch W of group q + 1
-#pragma unroll
-            for (int i = 0; i < NG - 1; ++i) {
-                r_q[i] = r_q[i + 1];
-                c_q[i] = c_q[i + 1];
-            }
-            load_idx(q + NG, r_q[NG - 1], c_q[NG - 1]);
-            bool single_next = single;
-            if (q + 1 < n) single_next = prefetch_w(r_q[0]);
-            // reduce, route, store
-            reduce_transposed<32, B>(acc, lane);
-            const float res = __shfl_sync(FULL, acc[0], (lane & (B - 1)) * (32 / B));
-            if (lane < B) store((g0 + q) * B + lane, res);
-            single = single_next;
+            for (int off = LPN / 2; off >= 1; off >>= 1) acc += __shfl_xor_sync(FULL, acc, off);
+            if (l == 0) store((g0 + q) * B + g, acc);
         }
     }
     if (timed_out) {
@@ -269,14 +264,25 @@ cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32
                            const float *W, const float *H, float *P, int64_t nnz, int sm_count,
                            unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
-    const size_t smem = (size_t)RING_WARPS * RING_NG * RingShape<C>::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
+    using R = RingShape<C>;
+    const size_t smem = (size_t)RING_WARPS * RING_NG * R::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
     auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL, HAS_HINT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool configured = false;  // one opt-in per instantiation and process
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
     if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
-    if (e != cudaSuccess) return e;
-    kern<<<(unsigned)sm_count, RING_WARPS * 32, smem, stream>>>(rows, cols, perm, sval, W, H, P, nnz, work_counter,
-                                                                dev_status);
+    // blocks of groups handed out dynamically: about four blocks per warp on small
+    // inputs, never fewer than 16 groups (the ring drains between blocks) or more than 128
+    const int64_t n_groups = nnz / R::B;
+    int64_t bg = n_groups / ((int64_t)sm_count * RING_WARPS * 4);
+    if (bg < 16) bg = 16;
+    if (bg > 128) bg = 128;
+    kern<<<(unsigned)sm_count, RING_WARPS * 32, smem, stream>>>(rows, cols, perm, sval, W, H, P, nnz, (int)bg,
+                                                                work_counter, dev_status);
     return cudaGetLastError();
 }
 
