@@ -147,6 +147,10 @@ typedef struct {
     int64_t n_nonempty_cols; /* -1 unless computed (sddmm_plan_count_cols)     */
     int64_t device_bytes;   /* device memory the plan owns                     */
     float plan_ms;          /* device time of the binning pass                 */
+    int32_t reserved0;
+    int64_t n_dense_cells;  /* 128 x 64 cells handed to the dense-cell kernel  */
+    int64_t n_dense_nnz;    /* nonzeros inside them                            */
+    int64_t n_hub_cols;     /* columns marked for L2 residency (ring kernel)   */
 } sddmm_plan_info;
 SDDMM_API int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info);
 

@@ -46,7 +46,9 @@ class PlanInfo(C.Structure):
     _fields_ = [("M", C.c_int64), ("N", C.c_int64), ("nnz", C.c_int64), ("K", C.c_int32),
                 ("panel_rows", C.c_int32), ("col_tile", C.c_int32), ("n_col_tiles", C.c_int32),
                 ("n_work_items", C.c_int64), ("n_nonempty_rows", C.c_int64),
-                ("n_nonempty_cols", C.c_int64), ("device_bytes", C.c_int64), ("plan_ms", C.c_float)]
+                ("n_nonempty_cols", C.c_int64), ("device_bytes", C.c_int64), ("plan_ms", C.c_float),
+                ("reserved0", C.c_int32), ("n_dense_cells", C.c_int64), ("n_dense_nnz", C.c_int64),
+                ("n_hub_cols", C.c_int64)]
 
 
 _lib = None

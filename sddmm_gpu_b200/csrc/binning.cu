@@ -441,6 +441,187 @@ cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t
 }
 
 // ---------------------------------------------------------------------------
+// Dense-cell classification
+// ---------------------------------------------------------------------------
+namespace {
+
+__global__ void cell_key_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
+                                int64_t n_col_blocks, unsigned long long *keys, int32_t *idx)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        keys[i] = (unsigned long long)(rows[i] / DENSE_CELL_ROWS) * (unsigned long long)n_col_blocks +
+                  (unsigned long long)(cols[i] / DENSE_CELL_COLS);
+        idx[i] = (int32_t)i;
+    }
+}
+struct KeyHead {
+    const unsigned long long *keys;
+    __device__ __forceinline__ int operator()(int j) const { return (j == 0 || keys[j] != keys[j - 1]) ? 1 : 0; }
+};
+struct KeyHeadPred {
+    const unsigned long long *keys;
+    __device__ __forceinline__ bool operator()(int j) const { return j == 0 || keys[j] != keys[j - 1]; }
+};
+// per non-empty cell: dense or not, and how many nonzeros it contributes to the dense arrays
+__global__ void classify_cells_kernel(const int32_t *__restrict__ cell_start, int n_cells, int min_count,
+                                      int32_t *dense_flag, int64_t *dense_cnt)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i <= n_cells; i += gridDim.x * blockDim.x) {
+        if (i == n_cells) { dense_flag[i] = 0; dense_cnt[i] = 0; continue; }
+        const int c = cell_start[i + 1] - cell_start[i];
+        const int d = c >= min_count ? 1 : 0;
+        dense_flag[i] = d;
+        dense_cnt[i] = d ? c : 0;
+    }
+}
+__global__ void fill_dense_kernel(const unsigned long long *__restrict__ keys_s, const int32_t *__restrict__ idx_s,
+                                  const int32_t *__restrict__ cellid /* inclusive head scan */,
+                                  const int32_t *__restrict__ cell_start, const int32_t *__restrict__ dense_flag,
+                                  const int32_t *__restrict__ dense_slot, const int64_t *__restrict__ dense_off,
+                                  const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
+                                  int64_t n_col_blocks, DenseCell *cells, int32_t *idx_d, uint16_t *rc_d,
+                                  unsigned char *is_dense)
+{
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nnz; j += (int64_t)gridDim.x * blockDim.x) {
+        const int ci = cellid[j] - 1;
+        if (!dense_flag[ci]) continue;
+        const unsigned long long key = keys_s[j];
+        const int32_t row0 = (int32_t)(key / (unsigned long long)n_col_blocks) * DENSE_CELL_ROWS;
+        const int32_t col0 = (int32_t)(key % (unsigned long long)n_col_blocks) * DENSE_CELL_COLS;
+        const int32_t start = cell_start[ci];
+        const int64_t pos = dense_off[ci] + (j - start);
+        const int32_t orig = idx_s[j];
+        idx_d[pos] = orig;
+        rc_d[pos] = (uint16_t)(((rows[orig] - row0) << 8) | (cols[orig] - col0));
+        is_dense[orig] = 1;
+        if (j == start) {
+            DenseCell c;
+            c.row0 = row0;
+            c.col0 = col0;
+            c.offset = dense_off[ci];
+            c.count = cell_start[ci + 1] - start;
+            c.reserved = 0;
+            cells[dense_slot[ci]] = c;
+        }
+    }
+}
+struct NotDense {
+    const unsigned char *is_dense;
+    __device__ __forceinline__ bool operator()(int j) const { return is_dense[j] == 0; }
+};
+
+}  // namespace
+
+void DensePlan::release()
+{
+    cudaFree(cells); cudaFree(idx); cudaFree(rc); cudaFree(rows_s); cudaFree(cols_s); cudaFree(perm_s);
+    cells = nullptr; idx = nullptr; rc = nullptr; rows_s = cols_s = perm_s = nullptr;
+    n_cells = n_dense_nnz = n_sparse = 0;
+}
+
+cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
+                              float min_density, float min_share, DensePlan *out, cudaStream_t stream)
+{
+    (void)M;
+    out->release();
+    if (nnz == 0) return cudaSuccess;
+    const int n = (int)nnz;
+    const int64_t n_col_blocks = (N + DENSE_CELL_COLS - 1) / DENSE_CELL_COLS;
+    const int min_count = (int)(min_density * DENSE_CELL_ROWS * DENSE_CELL_COLS);
+    thrust::counting_iterator<int> counting(0);
+
+    // 1. nonzeros sorted by cell (stable: row-major inside a cell)
+    Scratch keys;  // keys_in | keys_out (u64) | idx_in | idx_sorted | cellid (i32)
+    CK(keys.reserve((size_t)nnz * (8 + 8 + 4 + 4 + 4)));
+    unsigned long long *k_in = (unsigned long long *)keys.ptr, *k_s = k_in + nnz;
+    int32_t *i_in = (int32_t *)(k_s + nnz), *i_s = i_in + nnz, *cellid = i_s + nnz;
+    cell_key_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_rows, d_cols, nnz, n_col_blocks, k_in, i_in);
+    CK(cudaGetLastError());
+    int bits = 1;
+    {
+        const unsigned long long max_key = (unsigned long long)((M + DENSE_CELL_ROWS - 1) / DENSE_CELL_ROWS) * n_col_blocks;
+        while (bits < 64 && (1ull << bits) <= max_key) ++bits;
+    }
+    Scratch tmp;
+    size_t tb = 0;
+    CK(cub::DeviceRadixSort::SortPairs(nullptr, tb, k_in, k_s, i_in, i_s, n, 0, bits, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, k_in, k_s, i_in, i_s, n, 0, bits, stream));
+
+    // 2. non-empty cells: starts and the cell id of every sorted position
+    auto heads = thrust::make_transform_iterator(counting, KeyHead{k_s});
+    tb = 0;
+    CK(cub::DeviceScan::InclusiveSum(nullptr, tb, heads, cellid, n, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::InclusiveSum(tmp.ptr, tb, heads, cellid, n, stream));
+    int n_cells = 0;
+    CK(cudaMemcpyAsync(&n_cells, cellid + (nnz - 1), sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    Scratch cellbuf;  // cell_start i32[n+1] | dense_flag i32[n+1] | dense_slot i32[n+1] | dense_cnt i64[n+1] | dense_off i64[n+1] | n_sel
+    const size_t nc1 = (size_t)n_cells + 1;
+    CK(cellbuf.reserve(nc1 * (4 * 3 + 8 * 2) + 64));
+    int64_t *dense_cnt = (int64_t *)cellbuf.ptr, *dense_off = dense_cnt + nc1;
+    int32_t *cell_start = (int32_t *)(dense_off + nc1), *dense_flag = cell_start + nc1, *dense_slot = dense_flag + nc1;
+    int *d_n_sel = (int *)(dense_slot + nc1);
+    tb = 0;
+    CK(cub::DeviceSelect::If(nullptr, tb, counting, cell_start, d_n_sel, n, KeyHeadPred{k_s}, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceSelect::If(tmp.ptr, tb, counting, cell_start, d_n_sel, n, KeyHeadPred{k_s}, stream));
+    CK(cudaMemcpyAsync(cell_start + n_cells, &n, sizeof(int), cudaMemcpyHostToDevice, stream));
+
+    // 3. classify, offsets of the dense cells' nonzeros and slots of the dense cells
+    classify_cells_kernel<<<grid_for(nc1), TPB, 0, stream>>>(cell_start, n_cells, min_count, dense_flag, dense_cnt);
+    CK(cudaGetLastError());
+    tb = 0;
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, dense_cnt, dense_off, (int)nc1, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, dense_cnt, dense_off, (int)nc1, stream));
+    tb = 0;
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, dense_flag, dense_slot, (int)nc1, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, dense_flag, dense_slot, (int)nc1, stream));
+    int64_t n_dense_nnz = 0;
+    int n_dense_cells = 0;
+    CK(cudaMemcpyAsync(&n_dense_nnz, dense_off + n_cells, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    CK(cudaMemcpyAsync(&n_dense_cells, dense_slot + n_cells, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    if (n_dense_cells == 0 || (double)n_dense_nnz < (double)min_share * (double)nnz) return cudaSuccess;  // not worth a split
+
+    // 4. the dense arrays and the remainder
+    auto body = [&]() -> cudaError_t {
+        CK(cudaMalloc(&out->cells, sizeof(DenseCell) * (size_t)n_dense_cells));
+        CK(cudaMalloc(&out->idx, sizeof(int32_t) * (size_t)n_dense_nnz));
+        CK(cudaMalloc(&out->rc, sizeof(uint16_t) * (size_t)n_dense_nnz));
+        Scratch flags;
+        CK(flags.reserve((size_t)nnz));
+        CK(cudaMemsetAsync(flags.ptr, 0, (size_t)nnz, stream));
+        fill_dense_kernel<<<grid_for(nnz), TPB, 0, stream>>>(k_s, i_s, cellid, cell_start, dense_flag, dense_slot, dense_off,
+                                                            d_rows, d_cols, nnz, n_col_blocks, out->cells, out->idx,
+                                                            out->rc, (unsigned char *)flags.ptr);
+        CK(cudaGetLastError());
+        const int64_t n_sparse = nnz - n_dense_nnz;
+        if (n_sparse > 0) {
+            CK(cudaMalloc(&out->perm_s, sizeof(int32_t) * (size_t)n_sparse));
+            CK(cudaMalloc(&out->rows_s, sizeof(int32_t) * (size_t)n_sparse));
+            CK(cudaMalloc(&out->cols_s, sizeof(int32_t) * (size_t)n_sparse));
+            tb = 0;
+            CK(cub::DeviceSelect::If(nullptr, tb, counting, out->perm_s, d_n_sel, n, NotDense{(unsigned char *)flags.ptr}, stream));
+            CK(tmp.reserve(tb));
+            CK(cub::DeviceSelect::If(tmp.ptr, tb, counting, out->perm_s, d_n_sel, n, NotDense{(unsigned char *)flags.ptr}, stream));
+            gather2_kernel<<<grid_for(n_sparse), TPB, 0, stream>>>(out->perm_s, d_rows, d_cols, n_sparse, out->rows_s, out->cols_s);
+            CK(cudaGetLastError());
+        }
+        out->n_cells = n_dense_cells;
+        out->n_dense_nnz = n_dense_nnz;
+        out->n_sparse = n_sparse;
+        return cudaStreamSynchronize(stream);
+    };
+    cudaError_t e = body();
+    if (e != cudaSuccess) out->release();
+    return e;
+}
+
+// ---------------------------------------------------------------------------
 // Reference-layout tiling tables (test hook)
 // ---------------------------------------------------------------------------
 namespace {

@@ -59,6 +59,25 @@ cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t
                                    int64_t budget_bytes, int32_t *d_cols_hinted, int64_t *n_hub_cols,
                                    int *degree_threshold, cudaStream_t stream);
 
+// Dense-cell classification.  S is cut into cells of DENSE_CELL_ROWS x
+// DENSE_CELL_COLS; a cell holding at least min_density of its positions is
+// "dense" and is computed as a small dense product by the dense-cell kernel,
+// the nonzeros of all other cells form a row-sorted remainder that goes through
+// the gather kernels with a permutation.  Nothing is built (n_cells == 0) when
+// the dense cells would hold less than min_share of the nonzeros.
+struct DensePlan {
+    DenseCell *cells = nullptr;   // one descriptor per dense cell
+    int64_t n_cells = 0;
+    int32_t *idx = nullptr;       // input index of every dense-cell nonzero, grouped by cell, row-major inside
+    uint16_t *rc = nullptr;       // (row - row0) << 8 | (col - col0)
+    int64_t n_dense_nnz = 0;
+    int32_t *rows_s = nullptr, *cols_s = nullptr, *perm_s = nullptr;  // remainder: indices and input positions
+    int64_t n_sparse = 0;
+    void release();
+};
+cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
+                              float min_density, float min_share, DensePlan *out, cudaStream_t stream);
+
 // Reference-layout tiling tables (test hook); see sddmm_plan_export_tiling.
 struct TilingTables {
     int32_t *t_rows, *t_cols, *tiled_ind, *lastIdx_tile, *lastIdx_block_tile, *active_row, *n_actv_row;

@@ -22,6 +22,18 @@ struct WorkItem {
     int32_t reserved;
 };
 
+// A dense cell of S: rows [row0, row0 + DENSE_CELL_ROWS) x columns [col0, col0 +
+// DENSE_CELL_COLS) (clipped to the matrix), whose `count` nonzeros start at
+// `offset` in the plan's dense arrays.
+constexpr int DENSE_CELL_ROWS = 128;
+constexpr int DENSE_CELL_COLS = 64;
+struct DenseCell {
+    int64_t offset;
+    int32_t row0, col0;
+    int32_t count;
+    int32_t reserved;
+};
+
 // Device status word written by kernels whose bounded waits give up.
 enum DeviceStatus : int { DEV_OK = 0, DEV_MBARRIER_TIMEOUT = 1 };
 
@@ -62,6 +74,13 @@ bool ring_supports(int K);
 cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                         const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
+
+// Dense-cell kernel: every dense cell is computed as the 128 x 64 block
+// W[rows] * H[cols]^T in fp32 (register-tiled FMAs from shared memory), then the
+// cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).
+cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
+                               const float *sval, const float *W, const float *H, float *P, int64_t M, int64_t N,
+                               int K, int sm_count, cudaStream_t stream);
 
 // One-time per-process kernel attribute set-up (opt-in shared memory sizes).
 cudaError_t init_kernel_attributes(size_t smem_optin);

@@ -48,6 +48,12 @@ struct sddmm_plan_s {
     int64_t n_items = 0;
     int32_t *d_item_rows = nullptr;  // distinct rows of every item, concatenated
     int32_t *d_cols_hint = nullptr;  // processing-order columns with hub marks (ring kernel), or null
+    // dense cells + row-sorted remainder (single-tile plans of locally dense matrices)
+    DensePlan dense;
+    WorkItem *d_items_s = nullptr;
+    int64_t n_items_s = 0;
+    int32_t *d_item_rows_s = nullptr;
+    int64_t n_item_rows_s = 0;
     int64_t n_hub_cols = 0;
     int64_t n_item_rows = 0;
     int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
@@ -112,6 +118,9 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_items);
     cudaFree(p->d_item_rows);
     cudaFree(p->d_cols_hint);
+    p->dense.release();
+    cudaFree(p->d_items_s);
+    cudaFree(p->d_item_rows_s);
     cudaFree(p->d_W);
     cudaFree(p->d_H);
     cudaFree(p->d_S);
@@ -323,10 +332,28 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
     PLAN_TRY(build_work_items(rows_p, cols_p, nnz, p->cfg.panel_rows, p->col_tile, p->cfg.item_nnz, &p->d_items,
                               &p->n_items, &p->d_item_rows, &p->n_item_rows, s));
     p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items + sizeof(int32_t) * (size_t)p->n_item_rows);
+    // Locally dense matrices (many nonzeros per row): cells that are at least a
+    // quarter full go to the dense-cell kernel, if they hold a fifth of S or more.
+    // SDDMM_DENSE_CELLS=0 switches the classification off.
+    {
+        const char *env = std::getenv("SDDMM_DENSE_CELLS");
+        const bool enabled = !(env && std::atoi(env) == 0);
+        if (enabled && p->n_col_tiles == 1 && p->n_nonempty_rows > 0 && nnz / p->n_nonempty_rows >= 32) {
+            PLAN_TRY(build_dense_cells(p->d_rows, p->d_cols, nnz, M, N, 0.25f, 0.2f, &p->dense, s));
+            if (p->dense.n_cells > 0 && p->dense.n_sparse > 0 && !ring_supports(K)) {
+                PLAN_TRY(build_work_items(p->dense.rows_s, p->dense.cols_s, p->dense.n_sparse, p->cfg.panel_rows,
+                                          p->col_tile, p->cfg.item_nnz, &p->d_items_s, &p->n_items_s, &p->d_item_rows_s,
+                                          &p->n_item_rows_s, s));
+            }
+            if (p->dense.n_cells > 0)
+                p->device_bytes += (int64_t)(sizeof(DenseCell) * p->dense.n_cells + 6 * p->dense.n_dense_nnz +
+                                             12 * p->dense.n_sparse);
+        }
+    }
     // Hub-column marks for the ring kernel, when H is too large to live in L2 as a
     // whole.  SDDMM_L2_HUB_MB overrides the share of L2 set aside for hub rows (0 = off).
     if (ring_supports(K) && nnz > 0) {
-        int64_t budget_mb = 48;
+        int64_t budget_mb = 64;  // best of a 16..128 MB sweep on the scale-22 R-MAT matrix at K = 256
         if (const char *env = std::getenv("SDDMM_L2_HUB_MB")) budget_mb = std::atoll(env);
         const int64_t row_bytes = (int64_t)K * 4;
         if (budget_mb > 0 && N * row_bytes > budget_mb * (1ll << 20)) {
@@ -408,7 +435,19 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         return SDDMM_INVALID_ARG;
     }
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
-    if (use_gather) {
+    if (!forced && !tiled_out && p->dense.n_cells > 0) {
+        // locally dense plan: dense cells as small dense products, the rest gathered
+        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, dS, dW, dH, dP, p->M,
+                                       p->N, p->K, h->sm_count, s));
+        if (p->dense.n_sparse > 0) {
+            if (ring_supports(p->K))
+                CUDA_TRY(h, launch_ring(p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP, p->dense.n_sparse,
+                                        p->K, false, h->sm_count, h->d_work_counter, h->d_status, s));
+            else
+                CUDA_TRY(h, launch_panel(p->d_items_s, p->n_items_s, p->d_item_rows_s, p->dense.rows_s, p->dense.cols_s,
+                                         p->dense.perm_s, dS, dW, dH, dP, p->K, p->cfg, h->sm_count, h->d_status, s));
+        }
+    } else if (use_gather) {
         CUDA_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
     } else {
         const bool tiled = p->d_perm != nullptr;
@@ -504,6 +543,9 @@ int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info)
     info->n_nonempty_cols = p->n_nonempty_cols;
     info->device_bytes = p->device_bytes;
     info->plan_ms = p->plan_ms;
+    info->n_dense_cells = p->dense.n_cells;
+    info->n_dense_nnz = p->dense.n_dense_nnz;
+    info->n_hub_cols = p->n_hub_cols;
     return SDDMM_OK;
 }
 

@@ -64,6 +64,25 @@ def broadcast_h(H, src=0, group=None, chunks=1):
     return handles
 
 
+def upload_h_sharded(H_dev, H_host_slice, rank, world, group=None):
+    """Bring a host-resident H into every rank's device memory using all PCIe links:
+    rank r copies rows [r*n/world, (r+1)*n/world) of H from its pinned host slice to
+    its GPU, then the slices are exchanged over NVLink (one broadcast per slice, into
+    each GPU's own copy of H).  Returns nothing; H_dev is complete on return of the
+    collectives (stream-ordered)."""
+    n = H_dev.shape[0]
+    bounds = [(n * r) // world for r in range(world + 1)]
+    H_dev[bounds[rank]:bounds[rank + 1]].copy_(H_host_slice, non_blocking=True)
+    if world > 1:
+        for r in range(world):
+            if bounds[r + 1] > bounds[r]:
+                dist.broadcast(H_dev[bounds[r]:bounds[r + 1]], src=r, group=group)
+
+
+def h_slice_bounds(n, rank, world):
+    return (n * rank) // world, (n * (rank + 1)) // world
+
+
 def gather_p(P_local, shard, group=None):
     """All ranks' P slices concatenated in input order (optional; P normally stays sharded)."""
     if not dist.is_initialized() or shard.world == 1:

@@ -317,3 +317,47 @@ def test_cli_prints_reference_lines_and_matches_oracle(tmp_path):
     assert bad.returncode != 0 and bad.stderr.startswith("sddmm: ")
     bad = subprocess.run([exe, mtx, "30", "192", "50000"], capture_output=True, text=True)
     assert bad.returncode != 0 and "K must be" in bad.stderr
+
+
+# ---- dense cells: locally dense matrices split into dense blocks + gathered remainder ----
+
+@pytest.mark.parametrize("K", [16, 64, 100, 256])
+def test_dense_cell_path(engine, K):
+    p = synth.to_numpy(synth.attention_mask(M=1100, half_width=96, n_global=7, K=K, device="cpu"))
+    rng = np.random.default_rng(K)
+    vals = rng.standard_normal(p["rows"].shape[0]).astype(np.float32)
+    for sv in (vals, None):
+        P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], sv, 0)
+        assert info.n_dense_cells > 0 and 0 < info.n_dense_nnz <= info.nnz
+        assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], sv)
+    # a forced kernel bypasses the split and must agree
+    P2, _ = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], vals, api.FLAG_KERNEL_GATHER)
+    assert_parity(P2, p["rows"], p["cols"], p["W"], p["H"], vals)
+
+
+def test_dense_cells_cover_everything_or_nothing(engine):
+    # fully dense small matrix: the full cells are dense, the thin edge cells fall to the remainder
+    M, N, K = 200, 130, 32
+    rows = np.repeat(np.arange(M), N).astype(np.int32)
+    cols = np.tile(np.arange(N), M).astype(np.int32)
+    rng = np.random.default_rng(0)
+    W = rng.standard_normal((M, K)).astype(np.float32)
+    H = rng.standard_normal((N, K)).astype(np.float32)
+    P, info = run_plan(engine, M, N, rows, cols, W, H, None, 0)
+    assert info.n_dense_cells >= 2 and 128 * 128 <= info.n_dense_nnz < rows.shape[0]
+    assert_parity(P, rows, cols, W, H)
+    # sparse matrix with long rows but no dense cell: classification declines
+    rows, cols = random_coo(rng, 64, 60000, 64 * 40)
+    W = rng.standard_normal((64, K)).astype(np.float32)
+    H = rng.standard_normal((60000, K)).astype(np.float32)
+    P, info = run_plan(engine, 64, 60000, rows, cols, W, H, None, 0)
+    assert info.n_dense_cells == 0
+    assert_parity(P, rows, cols, W, H)
+
+
+@pytest.mark.parametrize("name", ["c2", "c5_small"])
+def test_benchmark_configs_default_path(engine, name):
+    p = _scaled(synth.bag_of_words) if name == "c2" else _scaled(synth.attention_mask, M=4096, half_width=64, n_global=12, K=64)
+    P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], 0,
+                       p["panel_rows"], p["col_tile"])
+    assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
