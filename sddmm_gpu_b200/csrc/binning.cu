@@ -9,6 +9,7 @@
 #include <thrust/iterator/counting_iterator.h>
 #include <thrust/iterator/transform_iterator.h>
 
+#include <algorithm>
 #include <climits>
 #include <vector>
 
@@ -442,15 +443,57 @@ cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t
 
 // ---------------------------------------------------------------------------
 // Dense-cell classification
+//
+// Three classes of cells, each 128 rows x 64 columns:
+//   class 0  rows that are (nearly) full -- "global" rows -- are compacted into
+//            virtual row panels (row r -> its rank among the dense rows);
+//   class 1  likewise for (nearly) full columns of the remaining nonzeros;
+//   class 2  the regular grid over everything else (bands, dense blocks).
+// A cell is handed to the dense-cell kernel when it holds at least min_density
+// of its 8192 positions.
 // ---------------------------------------------------------------------------
 namespace {
 
+__global__ void dense_line_flags_kernel(const int64_t *__restrict__ row_ptr, int64_t M, int64_t min_row_deg,
+                                        const int32_t *__restrict__ col_deg, int64_t N, int64_t min_col_deg,
+                                        int32_t *row_flag, int32_t *col_flag)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t r = t; r <= M; r += step) row_flag[r] = (r < M && row_ptr[r + 1] - row_ptr[r] >= min_row_deg) ? 1 : 0;
+    for (int64_t c = t; c <= N; c += step) col_flag[c] = (c < N && col_deg[c] >= min_col_deg) ? 1 : 0;
+}
+// flag + exclusive scan -> virtual id (or -1) and the compacted list
+__global__ void dense_line_ids_kernel(const int32_t *__restrict__ flag, const int32_t *__restrict__ rank, int64_t n,
+                                      int32_t *vid, int32_t *list)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        if (flag[i]) {
+            vid[i] = rank[i];
+            list[rank[i]] = (int32_t)i;
+        } else {
+            vid[i] = -1;
+        }
+    }
+}
+
+struct CellGeometry {
+    unsigned long long grid;  // keys per class: n_row_panels * n_col_blocks of the regular grid
+    int64_t ncb;              // column blocks of the matrix
+    int64_t nvcb;             // column blocks over the dense columns
+};
+
 __global__ void cell_key_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
-                                int64_t n_col_blocks, unsigned long long *keys, int32_t *idx)
+                                const int32_t *__restrict__ row_vid, const int32_t *__restrict__ col_vid,
+                                CellGeometry geo, unsigned long long *keys, int32_t *idx)
 {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
-        keys[i] = (unsigned long long)(rows[i] / DENSE_CELL_ROWS) * (unsigned long long)n_col_blocks +
-                  (unsigned long long)(cols[i] / DENSE_CELL_COLS);
+        const int32_t r = rows[i], c = cols[i];
+        const int32_t vr = row_vid[r], vc = col_vid[c];
+        unsigned long long key;
+        if (vr >= 0) key = (unsigned long long)(vr / DENSE_CELL_ROWS) * geo.ncb + (c / DENSE_CELL_COLS);
+        else if (vc >= 0) key = geo.grid + (unsigned long long)(r / DENSE_CELL_ROWS) * geo.nvcb + (vc / DENSE_CELL_COLS);
+        else key = 2 * geo.grid + (unsigned long long)(r / DENSE_CELL_ROWS) * geo.ncb + (c / DENSE_CELL_COLS);
+        keys[i] = key;
         idx[i] = (int32_t)i;
     }
 }
@@ -478,30 +521,37 @@ __global__ void fill_dense_kernel(const unsigned long long *__restrict__ keys_s,
                                   const int32_t *__restrict__ cellid /* inclusive head scan */,
                                   const int32_t *__restrict__ cell_start, const int32_t *__restrict__ dense_flag,
                                   const int32_t *__restrict__ dense_slot, const int64_t *__restrict__ dense_off,
-                                  const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
-                                  int64_t n_col_blocks, DenseCell *cells, int32_t *idx_d, uint16_t *rc_d,
+                                  const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
+                                  const int32_t *__restrict__ row_vid, const int32_t *__restrict__ col_vid, int64_t nnz,
+                                  CellGeometry geo, DenseCell *cells, int32_t *idx_d, uint16_t *rc_d,
                                   unsigned char *is_dense)
 {
     for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nnz; j += (int64_t)gridDim.x * blockDim.x) {
         const int ci = cellid[j] - 1;
         if (!dense_flag[ci]) continue;
         const unsigned long long key = keys_s[j];
-        const int32_t row0 = (int32_t)(key / (unsigned long long)n_col_blocks) * DENSE_CELL_ROWS;
-        const int32_t col0 = (int32_t)(key % (unsigned long long)n_col_blocks) * DENSE_CELL_COLS;
+        const int cls = (int)(key / geo.grid);
+        const unsigned long long rem = key % geo.grid;
+        const unsigned long long nb = (cls == 1) ? (unsigned long long)geo.nvcb : (unsigned long long)geo.ncb;
+        const int32_t row0 = (int32_t)(rem / nb) * DENSE_CELL_ROWS;  // virtual for class 0
+        const int32_t col0 = (int32_t)(rem % nb) * DENSE_CELL_COLS;  // virtual for class 1
         const int32_t start = cell_start[ci];
         const int64_t pos = dense_off[ci] + (j - start);
         const int32_t orig = idx_s[j];
+        const int32_t r = rows[orig], c = cols[orig];
+        const int32_t rl = (cls == 0 ? row_vid[r] : r) - row0;
+        const int32_t cl = (cls == 1 ? col_vid[c] : c) - col0;
         idx_d[pos] = orig;
-        rc_d[pos] = (uint16_t)(((rows[orig] - row0) << 8) | (cols[orig] - col0));
+        rc_d[pos] = (uint16_t)((rl << 8) | cl);
         is_dense[orig] = 1;
         if (j == start) {
-            DenseCell c;
-            c.row0 = row0;
-            c.col0 = col0;
-            c.offset = dense_off[ci];
-            c.count = cell_start[ci + 1] - start;
-            c.reserved = 0;
-            cells[dense_slot[ci]] = c;
+            DenseCell dcell;
+            dcell.row0 = row0;
+            dcell.col0 = col0;
+            dcell.offset = dense_off[ci];
+            dcell.count = cell_start[ci + 1] - start;
+            dcell.cls = cls;
+            cells[dense_slot[ci]] = dcell;
         }
     }
 }
@@ -515,35 +565,71 @@ struct NotDense {
 void DensePlan::release()
 {
     cudaFree(cells); cudaFree(idx); cudaFree(rc); cudaFree(rows_s); cudaFree(cols_s); cudaFree(perm_s);
+    cudaFree(dense_rows); cudaFree(dense_cols);
     cells = nullptr; idx = nullptr; rc = nullptr; rows_s = cols_s = perm_s = nullptr;
-    n_cells = n_dense_nnz = n_sparse = 0;
+    dense_rows = dense_cols = nullptr;
+    n_cells = n_dense_nnz = n_sparse = n_dense_rows = n_dense_cols = 0;
 }
 
-cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
-                              float min_density, float min_share, DensePlan *out, cudaStream_t stream)
+cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, const int64_t *d_row_ptr, int64_t nnz,
+                              int64_t M, int64_t N, float min_density, float min_share, DensePlan *out,
+                              cudaStream_t stream)
 {
-    (void)M;
     out->release();
     if (nnz == 0) return cudaSuccess;
     const int n = (int)nnz;
-    const int64_t n_col_blocks = (N + DENSE_CELL_COLS - 1) / DENSE_CELL_COLS;
     const int min_count = (int)(min_density * DENSE_CELL_ROWS * DENSE_CELL_COLS);
     thrust::counting_iterator<int> counting(0);
+    Scratch tmp;
+    size_t tb = 0;
+
+    // 0. dense rows and columns -> virtual ids and compacted lists
+    Scratch lines;  // col_deg[N] | row_flag[M+1] | row_rank[M+1] | col_flag[N+1] | col_rank[N+1] | row_vid[M] | col_vid[N]
+    const size_t m1 = (size_t)M + 1, n1 = (size_t)N + 1;
+    CK(lines.reserve(sizeof(int32_t) * ((size_t)N + 2 * m1 + 2 * n1 + (size_t)M + (size_t)N)));
+    int32_t *col_deg = (int32_t *)lines.ptr, *row_flag = col_deg + N, *row_rank = row_flag + m1;
+    int32_t *col_flag = row_rank + m1, *col_rank = col_flag + n1, *row_vid = col_rank + n1, *col_vid = row_vid + M;
+    CK(cudaMemsetAsync(col_deg, 0, sizeof(int32_t) * (size_t)N, stream));
+    col_degree_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols, nnz, col_deg);
+    const int64_t min_row_deg = std::max<int64_t>(N / 4, 4 * DENSE_CELL_COLS);
+    const int64_t min_col_deg = std::max<int64_t>(M / 4, 4 * DENSE_CELL_ROWS);
+    dense_line_flags_kernel<<<grid_for(std::max(M, N) + 1), TPB, 0, stream>>>(d_row_ptr, M, min_row_deg, col_deg, N,
+                                                                           min_col_deg, row_flag, col_flag);
+    CK(cudaGetLastError());
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, row_flag, row_rank, (int)m1, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, row_flag, row_rank, (int)m1, stream));
+    tb = 0;
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, col_flag, col_rank, (int)n1, stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, col_flag, col_rank, (int)n1, stream));
+    int n_dr = 0, n_dcol = 0;
+    CK(cudaMemcpyAsync(&n_dr, row_rank + M, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaMemcpyAsync(&n_dcol, col_rank + N, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    CK(cudaMalloc(&out->dense_rows, sizeof(int32_t) * (size_t)(n_dr > 0 ? n_dr : 1)));
+    CK(cudaMalloc(&out->dense_cols, sizeof(int32_t) * (size_t)(n_dcol > 0 ? n_dcol : 1)));
+    dense_line_ids_kernel<<<grid_for(M), TPB, 0, stream>>>(row_flag, row_rank, M, row_vid, out->dense_rows);
+    dense_line_ids_kernel<<<grid_for(N), TPB, 0, stream>>>(col_flag, col_rank, N, col_vid, out->dense_cols);
+    CK(cudaGetLastError());
+    out->n_dense_rows = n_dr;
+    out->n_dense_cols = n_dcol;
+
+    CellGeometry geo;
+    geo.ncb = (N + DENSE_CELL_COLS - 1) / DENSE_CELL_COLS;
+    geo.nvcb = std::max<int64_t>(1, (n_dcol + DENSE_CELL_COLS - 1) / DENSE_CELL_COLS);
+    geo.grid = (unsigned long long)((M + DENSE_CELL_ROWS - 1) / DENSE_CELL_ROWS) * (unsigned long long)geo.ncb;
 
     // 1. nonzeros sorted by cell (stable: row-major inside a cell)
     Scratch keys;  // keys_in | keys_out (u64) | idx_in | idx_sorted | cellid (i32)
     CK(keys.reserve((size_t)nnz * (8 + 8 + 4 + 4 + 4)));
     unsigned long long *k_in = (unsigned long long *)keys.ptr, *k_s = k_in + nnz;
     int32_t *i_in = (int32_t *)(k_s + nnz), *i_s = i_in + nnz, *cellid = i_s + nnz;
-    cell_key_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_rows, d_cols, nnz, n_col_blocks, k_in, i_in);
+    cell_key_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_rows, d_cols, nnz, row_vid, col_vid, geo, k_in, i_in);
     CK(cudaGetLastError());
     int bits = 1;
-    {
-        const unsigned long long max_key = (unsigned long long)((M + DENSE_CELL_ROWS - 1) / DENSE_CELL_ROWS) * n_col_blocks;
-        while (bits < 64 && (1ull << bits) <= max_key) ++bits;
-    }
-    Scratch tmp;
-    size_t tb = 0;
+    while (bits < 64 && (1ull << bits) <= 3 * geo.grid) ++bits;
+    tb = 0;
     CK(cub::DeviceRadixSort::SortPairs(nullptr, tb, k_in, k_s, i_in, i_s, n, 0, bits, stream));
     CK(tmp.reserve(tb));
     CK(cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, k_in, k_s, i_in, i_s, n, 0, bits, stream));
@@ -557,7 +643,7 @@ cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int6
     int n_cells = 0;
     CK(cudaMemcpyAsync(&n_cells, cellid + (nnz - 1), sizeof(int), cudaMemcpyDeviceToHost, stream));
     CK(cudaStreamSynchronize(stream));
-    Scratch cellbuf;  // cell_start i32[n+1] | dense_flag i32[n+1] | dense_slot i32[n+1] | dense_cnt i64[n+1] | dense_off i64[n+1] | n_sel
+    Scratch cellbuf;  // dense_cnt i64[n+1] | dense_off i64[n+1] | cell_start i32[n+1] | dense_flag i32[n+1] | dense_slot i32[n+1] | n_sel
     const size_t nc1 = (size_t)n_cells + 1;
     CK(cellbuf.reserve(nc1 * (4 * 3 + 8 * 2) + 64));
     int64_t *dense_cnt = (int64_t *)cellbuf.ptr, *dense_off = dense_cnt + nc1;
@@ -585,7 +671,10 @@ cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int6
     CK(cudaMemcpyAsync(&n_dense_nnz, dense_off + n_cells, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
     CK(cudaMemcpyAsync(&n_dense_cells, dense_slot + n_cells, sizeof(int), cudaMemcpyDeviceToHost, stream));
     CK(cudaStreamSynchronize(stream));
-    if (n_dense_cells == 0 || (double)n_dense_nnz < (double)min_share * (double)nnz) return cudaSuccess;  // not worth a split
+    if (n_dense_cells == 0 || (double)n_dense_nnz < (double)min_share * (double)nnz) {  // not worth a split
+        out->release();
+        return cudaSuccess;
+    }
 
     // 4. the dense arrays and the remainder
     auto body = [&]() -> cudaError_t {
@@ -596,8 +685,8 @@ cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int6
         CK(flags.reserve((size_t)nnz));
         CK(cudaMemsetAsync(flags.ptr, 0, (size_t)nnz, stream));
         fill_dense_kernel<<<grid_for(nnz), TPB, 0, stream>>>(k_s, i_s, cellid, cell_start, dense_flag, dense_slot, dense_off,
-                                                            d_rows, d_cols, nnz, n_col_blocks, out->cells, out->idx,
-                                                            out->rc, (unsigned char *)flags.ptr);
+                                                            d_rows, d_cols, row_vid, col_vid, nnz, geo, out->cells,
+                                                            out->idx, out->rc, (unsigned char *)flags.ptr);
         CK(cudaGetLastError());
         const int64_t n_sparse = nnz - n_dense_nnz;
         if (n_sparse > 0) {

@@ -60,11 +60,12 @@ cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t
                                    int *degree_threshold, cudaStream_t stream);
 
 // Dense-cell classification.  S is cut into cells of DENSE_CELL_ROWS x
-// DENSE_CELL_COLS; a cell holding at least min_density of its positions is
-// "dense" and is computed as a small dense product by the dense-cell kernel,
-// the nonzeros of all other cells form a row-sorted remainder that goes through
-// the gather kernels with a permutation.  Nothing is built (n_cells == 0) when
-// the dense cells would hold less than min_share of the nonzeros.
+// DENSE_CELL_COLS -- over compacted (nearly) full rows, then compacted (nearly)
+// full columns, then the regular grid; a cell holding at least min_density of its
+// positions is "dense" and is computed as a small dense product by the dense-cell
+// kernel, the nonzeros of all other cells form a row-sorted remainder that goes
+// through the gather kernels with a permutation.  Nothing is built (n_cells == 0)
+// when the dense cells would hold less than min_share of the nonzeros.
 struct DensePlan {
     DenseCell *cells = nullptr;   // one descriptor per dense cell
     int64_t n_cells = 0;
@@ -73,10 +74,13 @@ struct DensePlan {
     int64_t n_dense_nnz = 0;
     int32_t *rows_s = nullptr, *cols_s = nullptr, *perm_s = nullptr;  // remainder: indices and input positions
     int64_t n_sparse = 0;
+    int32_t *dense_rows = nullptr, *dense_cols = nullptr;  // ids of the compacted full rows / columns
+    int64_t n_dense_rows = 0, n_dense_cols = 0;
     void release();
 };
-cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t M, int64_t N,
-                              float min_density, float min_share, DensePlan *out, cudaStream_t stream);
+cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, const int64_t *d_row_ptr, int64_t nnz,
+                              int64_t M, int64_t N, float min_density, float min_share, DensePlan *out,
+                              cudaStream_t stream);
 
 // Reference-layout tiling tables (test hook); see sddmm_plan_export_tiling.
 struct TilingTables {

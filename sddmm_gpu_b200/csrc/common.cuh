@@ -23,15 +23,17 @@ struct WorkItem {
 };
 
 // A dense cell of S: rows [row0, row0 + DENSE_CELL_ROWS) x columns [col0, col0 +
-// DENSE_CELL_COLS) (clipped to the matrix), whose `count` nonzeros start at
-// `offset` in the plan's dense arrays.
+// DENSE_CELL_COLS) (clipped), whose `count` nonzeros start at `offset` in the
+// plan's dense arrays.  cls 0: row0 indexes the list of compacted full rows;
+// cls 1: col0 indexes the list of compacted full columns; cls 2: both are
+// plain matrix coordinates.
 constexpr int DENSE_CELL_ROWS = 128;
 constexpr int DENSE_CELL_COLS = 64;
 struct DenseCell {
     int64_t offset;
     int32_t row0, col0;
     int32_t count;
-    int32_t reserved;
+    int32_t cls;
 };
 
 // Device status word written by kernels whose bounded waits give up.
@@ -79,8 +81,9 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
 // W[rows] * H[cols]^T in fp32 (register-tiled FMAs from shared memory), then the
 // cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
-                               const float *sval, const float *W, const float *H, float *P, int64_t M, int64_t N,
-                               int K, int sm_count, cudaStream_t stream);
+                               const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
+                               int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
+                               int64_t M, int64_t N, int K, int sm_count, cudaStream_t stream);
 
 // One-time per-process kernel attribute set-up (opt-in shared memory sizes).
 cudaError_t init_kernel_attributes(size_t smem_optin);

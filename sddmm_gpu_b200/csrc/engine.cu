@@ -339,7 +339,7 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
         const char *env = std::getenv("SDDMM_DENSE_CELLS");
         const bool enabled = !(env && std::atoi(env) == 0);
         if (enabled && p->n_col_tiles == 1 && p->n_nonempty_rows > 0 && nnz / p->n_nonempty_rows >= 32) {
-            PLAN_TRY(build_dense_cells(p->d_rows, p->d_cols, nnz, M, N, 0.25f, 0.2f, &p->dense, s));
+            PLAN_TRY(build_dense_cells(p->d_rows, p->d_cols, p->d_row_ptr, nnz, M, N, 0.25f, 0.2f, &p->dense, s));
             if (p->dense.n_cells > 0 && p->dense.n_sparse > 0 && !ring_supports(K)) {
                 PLAN_TRY(build_work_items(p->dense.rows_s, p->dense.cols_s, p->dense.n_sparse, p->cfg.panel_rows,
                                           p->col_tile, p->cfg.item_nnz, &p->d_items_s, &p->n_items_s, &p->d_item_rows_s,
@@ -437,8 +437,9 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (!forced && !tiled_out && p->dense.n_cells > 0) {
         // locally dense plan: dense cells as small dense products, the rest gathered
-        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, dS, dW, dH, dP, p->M,
-                                       p->N, p->K, h->sm_count, s));
+        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.dense_rows,
+                                       p->dense.n_dense_rows, p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP,
+                                       p->M, p->N, p->K, h->sm_count, s));
         if (p->dense.n_sparse > 0) {
             if (ring_supports(p->K))
                 CUDA_TRY(h, launch_ring(p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP, p->dense.n_sparse,

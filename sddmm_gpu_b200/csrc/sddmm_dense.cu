@@ -6,14 +6,17 @@
 // cell touch only 128 rows of W and 64 rows of H.  The plan's classification pass
 // (binning.cu, build_dense_cells) hands such cells to this kernel, which computes
 // the whole block W[row0 .. row0+128) * H[col0 .. col0+64)^T as a small dense
-// product and then lets the cell's nonzeros pick their entries.
+// product and then lets the cell's nonzeros pick their entries.  Full rows and
+// full columns ("global" tokens) are compacted by the plan first, so a cell's
+// rows or columns may come through an index list instead of being consecutive.
 //
 // The product is plain fp32 FMA, register-tiled (each of the 256 threads owns an
-// 8 x 4 piece of the block; per k it reads 12 floats from shared memory for 32
-// FMAs), so results carry ordinary fp32 rounding -- no reduced-precision tensor
-// path is involved.  W and H are staged through shared memory in chunks of 32
-// along K, transposed so that the inner loop reads 128-bit vectors; positions
-// outside the matrix or beyond K are zero-filled.  After the last chunk the block
+// 8 x 4 piece of the block; per four k it reads twelve float4 from shared memory
+// for 128 FMAs), so results carry ordinary fp32 rounding -- no reduced-precision tensor
+// path is involved.  W and H are staged through shared memory in chunks of 64
+// along K with 16-byte asynchronous copies (cp.async), rows padded so that the
+// inner loop's 128-bit loads are conflict-free; positions outside the matrix or
+// beyond K are zero-filled.  After the last chunk the block
 // is parked in shared memory and the cell's nonzeros (grouped by cell, row-major
 // inside, by the plan) read block[r][c], scale by S and store to P at their
 // input positions.
@@ -32,29 +35,44 @@ namespace {
 
 constexpr int DR = DENSE_CELL_ROWS;  // 128
 constexpr int DC = DENSE_CELL_COLS;  // 64
-constexpr int KC = 32;               // K chunk
-constexpr int WT_STRIDE = DR + 4;    // floats; keeps rows 16-byte aligned, spreads banks
-constexpr int HT_STRIDE = DC + 4;
+constexpr int KC = 64;               // K chunk staged at a time
+constexpr int KS = KC + 4;           // row stride of the staged operands (floats): 16-byte aligned rows, banks spread
 constexpr int CT_STRIDE = DC + 1;
-constexpr int WT_FLOATS = KC * WT_STRIDE;
-constexpr int HT_FLOATS = KC * HT_STRIDE;
-constexpr int SMEM_FLOATS = DR * CT_STRIDE;  // the block; the staging buffers alias its start
-static_assert(WT_FLOATS + HT_FLOATS <= SMEM_FLOATS, "staging must fit under the block");
+constexpr int STAGE_FLOATS = (DR + DC) * KS;
+constexpr int BLOCK_FLOATS = DR * CT_STRIDE;  // the finished block; aliases the staging area
+constexpr int SMEM_FLOATS = STAGE_FLOATS > BLOCK_FLOATS ? STAGE_FLOATS : BLOCK_FLOATS;
 static_assert(DR == 128 && DC == 64, "thread tiling below assumes 128 x 64 cells and 256 threads");
 
-__global__ void __launch_bounds__(256)
-sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const int32_t *__restrict__ idx,
-                   const uint16_t *__restrict__ rc, const float *__restrict__ sval, const float *__restrict__ W,
-                   const float *__restrict__ H, float *__restrict__ P, int64_t M, int64_t N, int K)
+// 16-byte asynchronous copy global -> shared; src_bytes = 0 fills the 16 bytes with zeros.
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src, int src_bytes)
 {
-    __shared__ __align__(16) float smem[SMEM_FLOATS];
-    float *Wt = smem;              // [KC][WT_STRIDE]: Wt[k][r] = W[row0 + r][k0 + k]
-    float *Ht = smem + WT_FLOATS;  // [KC][HT_STRIDE]: Ht[k][c] = H[col0 + c][k0 + k]
-    float *Ct = smem;              // [DR][CT_STRIDE], after the last chunk
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)),
+                 "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(256, 3)
+sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const int32_t *__restrict__ idx,
+                   const uint16_t *__restrict__ rc, const int32_t *__restrict__ dense_rows, int64_t n_dense_rows,
+                   const int32_t *__restrict__ dense_cols, int64_t n_dense_cols, const float *__restrict__ sval,
+                   const float *__restrict__ W, const float *__restrict__ H, float *__restrict__ P, int64_t M,
+                   int64_t N, int K)
+{
+    extern __shared__ __align__(16) float smem[];
+    float *Ws = smem;            // [DR][KS]: Ws[r][k] = W[row0 + r][k0 + k]
+    float *Hs = smem + DR * KS;  // [DC][KS]: Hs[c][k] = H[col0 + c][k0 + k]
+    float *Ct = smem;            // [DR][CT_STRIDE], after the last chunk
 
     const int tid = threadIdx.x;
-    const int ty = tid >> 4;  // rows ty*8 .. ty*8+7
-    const int tx = tid & 15;  // cols tx*4 .. tx*4+3
+    // thread (ty, tx) owns rows ty + 16 i (i < 8) and columns tx + 16 j (j < 4): neighbouring
+    // threads read neighbouring rows of the staged operands, which keeps the 128-bit
+    // shared-memory loads free of bank conflicts
+    const int ty = tid >> 4;
+    const int tx = tid & 15;
 
     for (int64_t cell = blockIdx.x; cell < n_cells; cell += gridDim.x) {
         const DenseCell dc = cells[cell];
@@ -65,44 +83,44 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
         for (int k0 = 0; k0 < K; k0 += KC) {
-            // stage W: 128 rows x 32 floats = 1024 float4, four per thread
+            // stage W (128 x 64 floats = 2048 float4, eight per thread) and H (1024 float4, four per
+            // thread); rows outside the matrix and k beyond K arrive as zeros
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int f = tid + i * 256;
+                const int r = f >> 4, kq = (f & 15) * 4;
+                int64_t row = (int64_t)dc.row0 + r;
+                if (dc.cls == 0) row = row < n_dense_rows ? dense_rows[row] : M;  // compacted full rows
+                const bool ok = row < M && k0 + kq < K;
+                cp_async16(Ws + r * KS + kq, ok ? W + row * K + k0 + kq : W, ok ? 16 : 0);
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int f = tid + i * 256;
-                const int r = f >> 3, kq = (f & 7) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                const int64_t row = (int64_t)dc.row0 + r;
-                if (row < M && k0 + kq < K) v = __ldg(reinterpret_cast<const float4 *>(W + row * K + k0 + kq));
-                Wt[(kq + 0) * WT_STRIDE + r] = v.x;
-                Wt[(kq + 1) * WT_STRIDE + r] = v.y;
-                Wt[(kq + 2) * WT_STRIDE + r] = v.z;
-                Wt[(kq + 3) * WT_STRIDE + r] = v.w;
+                const int c = f >> 4, kq = (f & 15) * 4;
+                int64_t col = (int64_t)dc.col0 + c;
+                if (dc.cls == 1) col = col < n_dense_cols ? dense_cols[col] : N;  // compacted full columns
+                const bool ok = col < N && k0 + kq < K;
+                cp_async16(Hs + c * KS + kq, ok ? H + col * K + k0 + kq : H, ok ? 16 : 0);
             }
-            // stage H: 64 rows x 32 floats = 512 float4, two per thread
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int f = tid + i * 256;
-                const int c = f >> 3, kq = (f & 7) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                const int64_t col = (int64_t)dc.col0 + c;
-                if (col < N && k0 + kq < K) v = __ldg(reinterpret_cast<const float4 *>(H + col * K + k0 + kq));
-                Ht[(kq + 0) * HT_STRIDE + c] = v.x;
-                Ht[(kq + 1) * HT_STRIDE + c] = v.y;
-                Ht[(kq + 2) * HT_STRIDE + c] = v.z;
-                Ht[(kq + 3) * HT_STRIDE + c] = v.w;
-            }
+            cp_async_wait_all();
             __syncthreads();
-#pragma unroll 8
-            for (int k = 0; k < KC; ++k) {
-                const float4 a0 = *reinterpret_cast<const float4 *>(Wt + k * WT_STRIDE + ty * 8);
-                const float4 a1 = *reinterpret_cast<const float4 *>(Wt + k * WT_STRIDE + ty * 8 + 4);
-                const float4 b = *reinterpret_cast<const float4 *>(Ht + k * HT_STRIDE + tx * 4);
-                const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll 2
+            for (int kk = 0; kk < KC; kk += 4) {
+                float4 a[8], b[4];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4 *>(Ws + (ty + 16 * i) * KS + kk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4 *>(Hs + (tx + 16 * j) * KS + kk);
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+                    for (int j = 0; j < 4; ++j) {
+                        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                    }
             }
             __syncthreads();  // everyone is done with this chunk (and, after the last, with the staging area)
         }
@@ -110,11 +128,29 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) Ct[(ty * 8 + i) * CT_STRIDE + tx * 4 + j] = acc[i][j];
+            for (int j = 0; j < 4; ++j) Ct[(ty + 16 * i) * CT_STRIDE + tx + 16 * j] = acc[i][j];
         __syncthreads();
         const int32_t *cidx = idx + dc.offset;
         const uint16_t *crc = rc + dc.offset;
-        for (int i = tid; i < dc.count; i += 256) {
+        int i = tid;
+        for (; i + 768 < dc.count; i += 1024) {  // four independent nonzeros per thread and trip
+            unsigned code[4];
+            int32_t o[4];
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                code[u] = __ldcs(crc + i + u * 256);
+                o[u] = __ldcs(cidx + i + u * 256);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u] = Ct[(code[u] >> 8) * CT_STRIDE + (code[u] & 255u)];
+                if (sval) v[u] *= __ldg(sval + o[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) P[o[u]] = v[u];
+        }
+        for (; i < dc.count; i += 256) {
             const unsigned code = crc[i];
             const int32_t o = cidx[i];
             float v = Ct[(code >> 8) * CT_STRIDE + (code & 255u)];
@@ -128,13 +164,22 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 }  // namespace
 
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
-                               const float *sval, const float *W, const float *H, float *P, int64_t M, int64_t N,
-                               int K, int sm_count, cudaStream_t stream)
+                               const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
+                               int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
+                               int64_t M, int64_t N, int K, int sm_count, cudaStream_t stream)
 {
     if (n_cells == 0) return cudaSuccess;
-    int64_t blocks = (int64_t)sm_count * 4;
+    const size_t smem = sizeof(float) * SMEM_FLOATS;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sddmm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    int64_t blocks = (int64_t)sm_count * 3;
     if (blocks > n_cells) blocks = n_cells;
-    sddmm_dense_kernel<<<(unsigned)blocks, 256, 0, stream>>>(cells, n_cells, idx, rc, sval, W, H, P, M, N, K);
+    sddmm_dense_kernel<<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows, dense_cols,
+                                                                n_dense_cols, sval, W, H, P, M, N, K);
     return cudaGetLastError();
 }
 
