@@ -296,7 +296,8 @@ def main():
 
     # ---- sharding (identity at one GPU) --------------------------------------
     rows_host = rows.cpu().numpy()
-    shard = multi_gpu.make_shard(M, rows_host, world, rank, align_rows=32)
+    row_cost = float(os.environ.get("SDDMM_PART_ROW_COST", "0"))
+    shard = multi_gpu.make_shard(M, rows_host, world, rank, align_rows=32, row_cost=row_cost)
     a, b = shard.nnz_begin, shard.nnz_end
     l_rows = (rows[a:b] - shard.row_begin).contiguous()
     l_cols = cols[a:b].contiguous()
@@ -340,7 +341,11 @@ def main():
     step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
     total_ms = evs[0].elapsed_time(evs[-1])
     t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+    rank_ms = [total_ms / args.steps]
     if world > 1:
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        rank_ms = [float(x.item()) / args.steps for x in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms_max = float(t.item())
     ms_per_step = total_ms_max / args.steps
@@ -448,7 +453,8 @@ def main():
                        "l2": "inputs larger than L2 (no flush)" if 4 * K * (M + N) > 200e6 else "inputs fit L2",
                        "parallelism": f"nnz-balanced row blocks x{world}", "kernel": kernel_name,
                        "panel_rows": info.panel_rows, "work_items": info.n_work_items,
-                       "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms},
+                       "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms,
+                       "rank_ms_per_step": [round(x, 4) for x in rank_ms], "partition_row_cost": row_cost},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }

@@ -223,6 +223,17 @@ SDDMM_API int sddmm_partition_rows(int64_t M, int64_t nnz, const int32_t *rows,
                                    int n_parts, int align_rows, int64_t *cuts,
                                    int64_t *nnz_cuts);
 
+/*
+ * The same cuts with a cost model instead of plain nonzero counts: a prefix
+ * costs its nonzeros plus row_cost per non-empty row (a row of S costs one W row
+ * however few nonzeros it has, so blocks of short rows are more expensive per
+ * nonzero than blocks of long ones).  row_cost = 0 gives sddmm_partition_rows.
+ * No counterpart in the reference beyond make_CSC's plain nnz balance.
+ */
+SDDMM_API int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_t *rows, int n_parts,
+                                            int align_rows, double row_cost, int64_t *cuts,
+                                            int64_t *nnz_cuts);
+
 /* ---- Matrix Market I/O (host) -------------------------------------------- */
 
 /*

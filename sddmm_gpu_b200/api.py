@@ -30,7 +30,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_coo",
     "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
-    "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_mtx_open", "sddmm_mtx_read",
+    "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
 
@@ -83,6 +83,7 @@ def lib():
     L.sddmm_plan_export_row_ptr.argtypes = [vp, vp]
     L.sddmm_plan_export_tiling.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, vp, vp, vp, vp, C.POINTER(i32)]
     L.sddmm_partition_rows.argtypes = [i64, i64, vp, C.c_int, C.c_int, vp, vp]
+    L.sddmm_partition_rows_weighted.argtypes = [i64, i64, vp, C.c_int, C.c_int, C.c_double, vp, vp]
     L.sddmm_mtx_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
                                  C.c_char_p, C.c_int]
     L.sddmm_mtx_read.argtypes = [vp, vp, vp, vp]
@@ -256,12 +257,12 @@ def count_cols_noalloc(d_cols, N, device=0, cuda_stream=None, nnz=None):
 
 # ---- host-only helpers (no GPU needed) -------------------------------------
 
-def partition_rows(M, rows, n_parts, align_rows=1):
+def partition_rows(M, rows, n_parts, align_rows=1, row_cost=0.0):
     rows = np.ascontiguousarray(rows, np.int32)
     cuts = np.zeros(n_parts + 1, np.int64)
     nnz_cuts = np.zeros(n_parts + 1, np.int64)
-    st = lib().sddmm_partition_rows(M, rows.shape[0], rows.ctypes.data, n_parts, align_rows, cuts.ctypes.data,
-                                    nnz_cuts.ctypes.data)
+    st = lib().sddmm_partition_rows_weighted(M, rows.shape[0], rows.ctypes.data, n_parts, align_rows, float(row_cost),
+                                             cuts.ctypes.data, nnz_cuts.ctypes.data)
     if st != OK:
         raise SddmmError(st)
     return cuts, nnz_cuts

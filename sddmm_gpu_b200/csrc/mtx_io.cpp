@@ -267,17 +267,43 @@ int sddmm_coo_sort_rows(int64_t *M, int64_t *N, int64_t nnz, int32_t *rows, int3
 int sddmm_partition_rows(int64_t M, int64_t nnz, const int32_t *rows, int n_parts, int align_rows, int64_t *cuts,
                          int64_t *nnz_cuts)
 {
-    if (M < 0 || nnz < 0 || n_parts < 1 || !cuts || (nnz > 0 && !rows)) return SDDMM_INVALID_ARG;
+    return sddmm_partition_rows_weighted(M, nnz, rows, n_parts, align_rows, 0.0, cuts, nnz_cuts);
+}
+
+int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_t *rows, int n_parts, int align_rows,
+                                  double row_cost, int64_t *cuts, int64_t *nnz_cuts)
+{
+    if (M < 0 || nnz < 0 || n_parts < 1 || !cuts || (nnz > 0 && !rows) || row_cost < 0) return SDDMM_INVALID_ARG;
     if (align_rows < 1) align_rows = 1;
     cuts[0] = 0;
-    for (int g = 1; g < n_parts; ++g) {
-        const int64_t target = (int64_t)(((__int128)nnz * g) / n_parts);
-        // smallest row r whose prefix (nonzeros in rows < r) reaches the target
-        int64_t r = target > 0 ? (int64_t)rows[target - 1] + 1 : 0;
-        r = ((r + align_rows - 1) / align_rows) * align_rows;
-        if (r > M) r = M;
-        if (r < cuts[g - 1]) r = cuts[g - 1];
-        cuts[g] = r;
+    if (row_cost == 0.0) {
+        for (int g = 1; g < n_parts; ++g) {
+            const int64_t target = (int64_t)(((__int128)nnz * g) / n_parts);
+            // smallest row r whose prefix (nonzeros in rows < r) reaches the target
+            int64_t r = target > 0 ? (int64_t)rows[target - 1] + 1 : 0;
+            r = ((r + align_rows - 1) / align_rows) * align_rows;
+            if (r > M) r = M;
+            if (r < cuts[g - 1]) r = cuts[g - 1];
+            cuts[g] = r;
+        }
+    } else {
+        // cost of a prefix = its nonzeros + row_cost per non-empty row in it
+        int64_t n_rows_ne = 0;
+        for (int64_t i = 0; i < nnz; ++i) n_rows_ne += (i == 0 || rows[i] != rows[i - 1]);
+        const double total = (double)nnz + row_cost * (double)n_rows_ne;
+        int g = 1;
+        double acc = 0;
+        for (int64_t i = 0; i < nnz && g < n_parts; ++i) {
+            acc += 1.0 + ((i == 0 || rows[i] != rows[i - 1]) ? row_cost : 0.0);
+            while (g < n_parts && acc >= total * g / n_parts) {
+                int64_t r = (int64_t)rows[i] + 1;
+                r = ((r + align_rows - 1) / align_rows) * align_rows;
+                if (r > M) r = M;
+                if (r < cuts[g - 1]) r = cuts[g - 1];
+                cuts[g++] = r;
+            }
+        }
+        for (; g < n_parts; ++g) cuts[g] = cuts[g - 1] > 0 ? cuts[g - 1] : 0;
     }
     cuts[n_parts] = M;
     if (nnz_cuts) {

@@ -37,10 +37,11 @@ class RowShard:
         return self.nnz_end - self.nnz_begin
 
 
-def make_shard(M, rows_host, world, rank, align_rows=32):
-    """nnz-balanced row cuts (sddmm_partition_rows) -> this rank's shard.
-    rows_host: the row index of every nonzero (row-sorted), numpy int32."""
-    cuts, nnz_cuts = api.partition_rows(M, rows_host, world, align_rows)
+def make_shard(M, rows_host, world, rank, align_rows=32, row_cost=0.0):
+    """Balanced row cuts (sddmm_partition_rows_weighted) -> this rank's shard.
+    rows_host: the row index of every nonzero (row-sorted), numpy int32.
+    row_cost: extra cost of a non-empty row, in nonzeros (0 = balance nonzeros only)."""
+    cuts, nnz_cuts = api.partition_rows(M, rows_host, world, align_rows, row_cost)
     return RowShard(rank, world, cuts, nnz_cuts)
 
 

@@ -155,3 +155,20 @@ def test_partition_rows_balanced_and_order_preserving(parts):
         r0 = cuts[g]
         pieces.append(oracle.cpu.sddmm_coo(rows[a:b] - r0, cols[a:b], W[r0:cuts[g + 1]], H) if b > a else np.zeros(0, np.float32))
     assert np.array_equal(np.concatenate(pieces), full)
+
+
+def test_weighted_partition_moves_cuts_towards_short_rows():
+    # first half: 100 rows of 100 nonzeros; second half: 10000 rows of 1 nonzero.  Same nonzero count,
+    # very different row counts: with a row cost the second block must get fewer nonzeros.
+    rows = np.concatenate([np.repeat(np.arange(100), 100), 100 + np.arange(10000)]).astype(np.int32)
+    M = 10100
+    cuts0, nnz0 = api.partition_rows(M, rows, 2, 1)
+    assert nnz0[1] == 10000 and cuts0[1] == 100
+    cuts1, nnz1 = api.partition_rows(M, rows, 2, 1, row_cost=1.0)
+    assert cuts1[1] > 100 and nnz1[1] > 10000
+    # cost of both sides within one row of each other
+    cost = lambda a, b: (b - a) + 1.0 * np.unique(rows[a:b]).size
+    assert abs(cost(0, nnz1[1]) - cost(nnz1[1], rows.size)) <= 4
+    for parts in (3, 8):
+        c, z = api.partition_rows(M, rows, parts, 32, row_cost=2.0)
+        assert c[0] == 0 and c[-1] == M and np.all(np.diff(c) >= 0) and z[-1] == rows.size
