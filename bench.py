@@ -154,7 +154,7 @@ def hbm_peak():
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (keyed by workload and kernel; full-size captures, 1-pass metrics)
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    ("c4_rmat_scale22_ef24_K256", "ring"): 55_959_587_072 + 392_071_680,   # profiles/sddmm_ring_kernel_c4_rmat_scale22_K256.md
+    ("c4_rmat_scale22_ef24_K256", "ring"): 47_011_806_208 + 391_284_992,   # profiles/sddmm_ring_kernel_c4_rmat_scale22_K256.md
     ("c4_rmat_scale22_ef24_K256", "panel"): 56_620_000_000 + 697_190_000,  # profiles/sddmm_panel_and_gather_kernels_rmat_K256.md
 }
 

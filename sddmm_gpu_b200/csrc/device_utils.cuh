@@ -94,6 +94,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity)
 // sleep so that a waiting warp does not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, unsigned parity)
 {
+#pragma unroll 1
     for (int it = 0; it < MBAR_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(it < 16 ? 32 : 256);

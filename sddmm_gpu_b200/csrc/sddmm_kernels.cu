@@ -380,8 +380,12 @@ cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t
                            int sm_count, int *dev_status, cudaStream_t stream)
 {
     auto kern = sddmm_panel_kernel<L, C, B, PANEL_WARPS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);
-    if (e != cudaSuccess) return e;
+    static size_t configured_smem = 0;  // largest opt-in made so far for this instantiation
+    if (cfg.smem_bytes > configured_smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);
+        if (e != cudaSuccess) return e;
+        configured_smem = cfg.smem_bytes;
+    }
     int64_t blocks = (int64_t)sm_count * cfg.ctas_per_sm;
     if (blocks > n_items) blocks = n_items;
     if (blocks < 1) blocks = 1;
