@@ -454,7 +454,9 @@ def main():
                        "parallelism": f"nnz-balanced row blocks x{world}", "kernel": kernel_name,
                        "panel_rows": info.panel_rows, "work_items": info.n_work_items,
                        "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms,
-                       "rank_ms_per_step": [round(x, 4) for x in rank_ms], "partition_row_cost": row_cost},
+                       "rank_ms_per_step": [round(x, 4) for x in rank_ms], "partition_row_cost": row_cost,
+                       "dense_cells": info.n_dense_cells, "dense_cell_nnz": info.n_dense_nnz,
+                       "hub_columns": info.n_hub_cols},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }

@@ -135,6 +135,16 @@ SDDMM_API int sddmm_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz,
                         const int32_t *rows, const int32_t *cols, const float *Sval,
                         const float *W, const float *H, int K, float *P);
 
+/*
+ * Self-test of the failure path (no counterpart in the reference, whose waits
+ * are unbounded): launches one warp that waits, with a short poll limit, on a
+ * barrier nothing arrives on.  The warp gives up after a few milliseconds and
+ * the call returns SDDMM_DEVICE_TIMEOUT -- the status a real kernel reports when
+ * one of its bounded waits runs out.  Nothing faults or hangs; the handle stays
+ * usable.
+ */
+SDDMM_API int sddmm_selftest_wait_timeout(sddmm_handle_t h);
+
 /* Sizes of what the binning pass built (test and reporting hook). */
 typedef struct {
     int64_t M, N, nnz;

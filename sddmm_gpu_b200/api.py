@@ -29,7 +29,7 @@ PLAN_DEVICE_INDICES = 0x2
 EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_coo",
-    "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
+    "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
@@ -77,6 +77,7 @@ def lib():
     L.sddmm_execute.argtypes = [vp, vp, vp, vp, vp, u32]
     L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
     L.sddmm_coo.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, vp]
+    L.sddmm_selftest_wait_timeout.argtypes = [vp]
     L.sddmm_plan_get_info.argtypes = [vp, C.POINTER(PlanInfo)]
     L.sddmm_plan_count_cols.argtypes = [vp, C.POINTER(i64)]
     L.sddmm_count_cols_noalloc.argtypes = [C.c_int, vp, i64, i64, vp, C.POINTER(i64), C.c_char_p, C.c_int]
@@ -144,6 +145,10 @@ class Handle:
     def _check(self, st):
         if st != OK:
             raise SddmmError(st, self.last_error())
+
+    def selftest_wait_timeout(self):
+        """Status of a wait that is made to run out (expected: DEVICE_TIMEOUT)."""
+        return lib().sddmm_selftest_wait_timeout(self._h)
 
     def set_stream(self, cuda_stream):
         """cuda_stream: integer cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream) or None."""

@@ -85,7 +85,9 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, int sm_count, cudaStream_t stream);
 
-// One-time per-process kernel attribute set-up (opt-in shared memory sizes).
-cudaError_t init_kernel_attributes(size_t smem_optin);
+// Self-test of the bounded-wait path: one warp waits (with a short poll limit) on
+// an mbarrier that nothing ever arrives on, gives up, records DEV_MBARRIER_TIMEOUT
+// in *dev_status and returns normally.  Nothing faults, traps or hangs.
+cudaError_t launch_wait_timeout_probe(int *dev_status, cudaStream_t stream);
 
 }  // namespace sddmm

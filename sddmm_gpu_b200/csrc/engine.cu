@@ -333,13 +333,14 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
                               &p->n_items, &p->d_item_rows, &p->n_item_rows, s));
     p->device_bytes += (int64_t)(sizeof(WorkItem) * (size_t)p->n_items + sizeof(int32_t) * (size_t)p->n_item_rows);
     // Locally dense matrices (many nonzeros per row): cells that are at least a
-    // quarter full go to the dense-cell kernel, if they hold a fifth of S or more.
+    // quarter full go to the dense-cell kernel, if they hold half of S or more
+    // (below that the second launch and the permuted remainder cost more than they save).
     // SDDMM_DENSE_CELLS=0 switches the classification off.
     {
         const char *env = std::getenv("SDDMM_DENSE_CELLS");
         const bool enabled = !(env && std::atoi(env) == 0);
         if (enabled && p->n_col_tiles == 1 && p->n_nonempty_rows > 0 && nnz / p->n_nonempty_rows >= 32) {
-            PLAN_TRY(build_dense_cells(p->d_rows, p->d_cols, p->d_row_ptr, nnz, M, N, 0.25f, 0.2f, &p->dense, s));
+            PLAN_TRY(build_dense_cells(p->d_rows, p->d_cols, p->d_row_ptr, nnz, M, N, 0.25f, 0.5f, &p->dense, s));
             if (p->dense.n_cells > 0 && p->dense.n_sparse > 0 && !ring_supports(K)) {
                 PLAN_TRY(build_work_items(p->dense.rows_s, p->dense.cols_s, p->dense.n_sparse, p->cfg.panel_rows,
                                           p->col_tile, p->cfg.item_nnz, &p->d_items_s, &p->n_items_s, &p->d_item_rows_s,
@@ -530,6 +531,17 @@ int sddmm_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const int32_t
     if (!p_dev) CUDA_TRY(h, cudaMemcpyAsync(P, dp, sizeof(float) * nnz, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(h, cudaStreamSynchronize(s));
     return SDDMM_OK;
+}
+
+int sddmm_selftest_wait_timeout(sddmm_handle_t h)
+{
+    if (!h) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = h->stream;
+    CUDA_TRY(h, launch_wait_timeout_probe(h->d_status, s));
+    CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(h, cudaStreamSynchronize(s));
+    return check_device_status(h);
 }
 
 int sddmm_plan_get_info(sddmm_plan_t p, sddmm_plan_info *info)

@@ -458,6 +458,30 @@ PanelConfig choose_panel_config(int K, int panel_rows_hint, int sm_count, size_t
     return cfg;
 }
 
-cudaError_t init_kernel_attributes(size_t) { return cudaSuccess; }
+namespace {
+// The wait that is meant to run out: same try_wait + back-off loop as the real
+// kernels, with a poll limit of a few thousand (a few milliseconds at most).
+__global__ void wait_timeout_probe_kernel(int *dev_status)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    bool done = false;
+    for (int it = 0; it < 4096 && !done; ++it) {
+        done = mbar_try_wait(&bar, 0);
+        if (!done) __nanosleep(256);
+    }
+    if (!done && threadIdx.x == 0) atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT);
+}
+}  // namespace
+
+cudaError_t launch_wait_timeout_probe(int *dev_status, cudaStream_t stream)
+{
+    wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(dev_status);
+    return cudaGetLastError();
+}
 
 }  // namespace sddmm

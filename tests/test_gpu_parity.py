@@ -361,3 +361,17 @@ def test_benchmark_configs_default_path(engine, name):
     P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], 0,
                        p["panel_rows"], p["col_tile"])
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+
+
+# ---- failure path: a bounded device wait that runs out ------------------------
+
+def test_bounded_wait_reports_timeout_and_handle_survives(engine):
+    # one warp waits on a barrier nothing sets, with a short limit; it gives up and the host
+    # sees DEVICE_TIMEOUT.  No fault, trap or hang is involved; the context stays usable.
+    assert engine.selftest_wait_timeout() == api.DEVICE_TIMEOUT
+    assert "wait" in engine.last_error()
+    rows = np.array([0, 1, 2], np.int32)
+    cols = np.array([0, 1, 2], np.int32)
+    W = np.ones((3, 128), np.float32)
+    P, _ = run_plan(engine, 3, 3, rows, cols, W, W, None, 0)
+    assert np.array_equal(P, np.full(3, 128.0, np.float32))
