@@ -78,12 +78,12 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
 
 // Dense-cell kernel: every dense cell is computed as the 128 x 64 block
-// W[rows] * H[cols]^T in fp32 (register-tiled FMAs from shared memory), then the
-// cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).
+// W[rows] * H[cols]^T -- fp32 FMAs, or (tensor) 3xTF32 on the tensor cores -- then
+// the cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
                                const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
-                               int64_t M, int64_t N, int K, int sm_count, cudaStream_t stream);
+                               int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream);
 
 // Self-test of the bounded-wait path: one warp waits (with a short poll limit) on
 // an mbarrier that nothing ever arrives on, gives up, records DEV_MBARRIER_TIMEOUT

@@ -29,6 +29,7 @@ struct sddmm_handle_s {
     unsigned long long *d_work_counter = nullptr;  // dynamic work distribution of the ring kernel
     int *h_status = nullptr;  // pinned mirror
     std::string last_error;
+    bool dense_tensor = true;  // dense cells on the tensor cores (3xTF32); SDDMM_DENSE_TENSOR=0 selects fp32 FMA
 };
 
 struct sddmm_plan_s {
@@ -200,6 +201,7 @@ int sddmm_create(sddmm_handle_t *out, int device)
     }
     *h->h_status = DEV_OK;
     h->stream = h->own_stream;
+    if (const char *env = std::getenv("SDDMM_DENSE_TENSOR")) h->dense_tensor = std::atoi(env) != 0;
     *out = h;
     return SDDMM_OK;
 }
@@ -440,7 +442,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         // locally dense plan: dense cells as small dense products, the rest gathered
         CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.dense_rows,
                                        p->dense.n_dense_rows, p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP,
-                                       p->M, p->N, p->K, h->sm_count, s));
+                                       p->M, p->N, p->K, h->dense_tensor, h->sm_count, s));
         if (p->dense.n_sparse > 0) {
             if (ring_supports(p->K))
                 CUDA_TRY(h, launch_ring(p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP, p->dense.n_sparse,

@@ -10,10 +10,11 @@
 // full columns ("global" tokens) are compacted by the plan first, so a cell's
 // rows or columns may come through an index list instead of being consecutive.
 //
-// The product is plain fp32 FMA, register-tiled (each of the 256 threads owns an
-// 8 x 4 piece of the block; per four k it reads twelve float4 from shared memory
-// for 128 FMAs), so results carry ordinary fp32 rounding -- no reduced-precision tensor
-// path is involved.  W and H are staged through shared memory in chunks of 64
+// The product runs either on the tensor cores as 3xTF32 (every fp32 operand split
+// into a TF32 head and tail, three mma.sync.m16n8k8 per product, fp32
+// accumulation: fp32-level accuracy) or as plain fp32 FMA, register-tiled (each
+// of the 256 threads owns an 8 x 4 piece of the block; per four k it reads twelve
+// float4 from shared memory for 128 FMAs).  W and H are staged through shared memory in chunks of 64
 // along K with 16-byte asynchronous copies (cp.async), rows padded so that the
 // inner loop's 128-bit loads are conflict-free; positions outside the matrix or
 // beyond K are zero-filled.  After the last chunk the block
@@ -55,6 +56,26 @@ __device__ __forceinline__ void cp_async_wait_all()
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
+// 3xTF32: an fp32 value x is split into hi = tf32(x) and lo = tf32(x - hi); the
+// product a*b is accumulated as lo_a*hi_b + hi_a*lo_b + hi_a*hi_b in fp32 by
+// three tensor-core MMAs, which keeps the error of the products at the 2^-21
+// level instead of TF32's 2^-11.
+__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo)
+{
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float rest = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// TENSOR = false: fp32 FMA, register tile 8 x 4 per thread.
+// TENSOR = true : 3xTF32 on the tensor cores (mma.sync m16n8k8), warp tile 32 x 32.
+template <bool TENSOR>
 __global__ void __launch_bounds__(256, 3)
 sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const int32_t *__restrict__ idx,
                    const uint16_t *__restrict__ rc, const int32_t *__restrict__ dense_rows, int64_t n_dense_rows,
@@ -76,7 +97,7 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 
     for (int64_t cell = blockIdx.x; cell < n_cells; cell += gridDim.x) {
         const DenseCell dc = cells[cell];
-        float acc[8][4];
+        float acc[8][4];  // FMA path: [row i][col j]; tensor path: [m-tile*4 + n-tile][fragment register]
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -105,30 +126,80 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
             }
             cp_async_wait_all();
             __syncthreads();
+            if constexpr (TENSOR) {
+                // warp (wr, wc) of a 4 x 2 grid owns rows wr*32 .. +32 and columns wc*32 .. +32 of the block:
+                // two m16 tiles x four n8 tiles.  Fragment element (row, k) sits at Ws[row][k], (k, n) at
+                // Hs[n][k]; with a row stride of 68 floats the 32 lanes of a fragment load hit 32 banks.
+                const int lane = tid & 31, warp = tid >> 5;
+                const int wr = warp >> 1, wc = warp & 1;
+                const int fr = lane >> 2, fk = lane & 3;
 #pragma unroll 2
-            for (int kk = 0; kk < KC; kk += 4) {
-                float4 a[8], b[4];
+                for (int kk = 0; kk < KC; kk += 8) {
+                    uint32_t a_hi[2][4], a_lo[2][4], b_hi[4][2], b_lo[4][2];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4 *>(Ws + (ty + 16 * i) * KS + kk);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4 *>(Hs + (tx + 16 * j) * KS + kk);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
-                        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
-                        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
-                        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                    for (int mt = 0; mt < 2; ++mt) {
+                        const float *p = Ws + (wr * 32 + mt * 16 + fr) * KS + kk + fk;
+                        split_tf32(p[0], a_hi[mt][0], a_lo[mt][0]);
+                        split_tf32(p[8 * KS], a_hi[mt][1], a_lo[mt][1]);
+                        split_tf32(p[4], a_hi[mt][2], a_lo[mt][2]);
+                        split_tf32(p[8 * KS + 4], a_hi[mt][3], a_lo[mt][3]);
                     }
-            }
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        const float *p = Hs + (wc * 32 + nt * 8 + fr) * KS + kk + fk;
+                        split_tf32(p[0], b_hi[nt][0], b_lo[nt][0]);
+                        split_tf32(p[4], b_hi[nt][1], b_lo[nt][1]);
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt) {
+                            mma_tf32(acc[mt * 4 + nt], a_lo[mt], b_hi[nt]);
+                            mma_tf32(acc[mt * 4 + nt], a_hi[mt], b_lo[nt]);
+                            mma_tf32(acc[mt * 4 + nt], a_hi[mt], b_hi[nt]);
+                        }
+                }
+            } else {
+#pragma unroll 2
+                for (int kk = 0; kk < KC; kk += 4) {
+                    float4 a[8], b[4];
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4 *>(Ws + (ty + 16 * i) * KS + kk);
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4 *>(Hs + (tx + 16 * j) * KS + kk);
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i)
+    #pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+                            acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+                            acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+                            acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                        }
+                }
+}
             __syncthreads();  // everyone is done with this chunk (and, after the last, with the staging area)
         }
         // park the block, then let the nonzeros pick their entries
+        if constexpr (TENSOR) {
+            const int lane = tid & 31, warp = tid >> 5;
+            const int wr = warp >> 1, wc = warp & 1;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+            for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) Ct[(ty + 16 * i) * CT_STRIDE + tx + 16 * j] = acc[i][j];
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int r = wr * 32 + mt * 16 + (lane >> 2), c = wc * 32 + nt * 8 + (lane & 3) * 2;
+                    Ct[r * CT_STRIDE + c] = acc[mt * 4 + nt][0];
+                    Ct[r * CT_STRIDE + c + 1] = acc[mt * 4 + nt][1];
+                    Ct[(r + 8) * CT_STRIDE + c] = acc[mt * 4 + nt][2];
+                    Ct[(r + 8) * CT_STRIDE + c + 1] = acc[mt * 4 + nt][3];
+                }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) Ct[(ty + 16 * i) * CT_STRIDE + tx + 16 * j] = acc[i][j];
+        }
         __syncthreads();
         const int32_t *cidx = idx + dc.offset;
         const uint16_t *crc = rc + dc.offset;
@@ -166,20 +237,26 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
                                const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
-                               int64_t M, int64_t N, int K, int sm_count, cudaStream_t stream)
+                               int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream)
 {
     if (n_cells == 0) return cudaSuccess;
     const size_t smem = sizeof(float) * SMEM_FLOATS;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(sddmm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(sddmm_dense_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(sddmm_dense_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     int64_t blocks = (int64_t)sm_count * 3;
     if (blocks > n_cells) blocks = n_cells;
-    sddmm_dense_kernel<<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows, dense_cols,
-                                                                n_dense_cols, sval, W, H, P, M, N, K);
+    if (tensor)
+        sddmm_dense_kernel<true><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows,
+                                                                          dense_cols, n_dense_cols, sval, W, H, P, M, N, K);
+    else
+        sddmm_dense_kernel<false><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows,
+                                                                           dense_cols, n_dense_cols, sval, W, H, P, M, N, K);
     return cudaGetLastError();
 }
 
