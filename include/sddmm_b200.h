@@ -51,7 +51,7 @@ enum {
 #define SDDMM_FLAG_TILED_ORDER  0x2u /* P in the plan's tiled order (what the reference's sddmm_GPU leaves in d_val, sddmm.cu:119) instead of input order */
 #define SDDMM_FLAG_KERNEL_GATHER 0x10u /* force the planless gather kernel */
 #define SDDMM_FLAG_KERNEL_PANEL  0x20u /* force the TMA-staged row-panel kernel */
-#define SDDMM_FLAG_KERNEL_RING   0x40u /* force the TMA gather-ring kernel (K = 128, 256, 512 or 1024) */
+#define SDDMM_FLAG_KERNEL_RING   0x40u /* force the shared-memory gather-ring kernels (K = 32, 64, 128, 256, 512 or 1024) */
 
 /* ---- plan flags ---------------------------------------------------------- */
 #define SDDMM_PLAN_SKIP_VALIDATION 0x1u /* trust sortedness and bounds (the reference checks neither) */

@@ -70,7 +70,8 @@ cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *
 
 // Ring kernel: H rows gathered by bulk asynchronous copies (TMA) into per-warp
 // shared-memory rings, work handed out dynamically through *work_counter (one
-// device word, zeroed by the launcher).  K must satisfy ring_supports(K).
+// device word, zeroed by the launcher).  K must satisfy ring_supports(K)
+// (32, 64, 128, 256, 512, 1024).
 bool ring_supports(int K);
 // cols_hinted: bit 31 of every column index marks a hub column (see build_hub_column_hints).
 cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
@@ -84,6 +85,12 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
                                const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream);
+
+// Ring kernel for short rows (K = 32, 64): the same per-warp rings filled with
+// 16-byte cp.async copies; reached through launch_ring.
+cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
+                              const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted,
+                              int sm_count, unsigned long long *work_counter, cudaStream_t stream);
 
 // Self-test of the bounded-wait path: one warp waits (with a short poll limit) on
 // an mbarrier that nothing ever arrives on, gives up, records DEV_MBARRIER_TIMEOUT

@@ -15,7 +15,7 @@ from sddmm_gpu_b200 import api, synth
 pytestmark = pytest.mark.gpu
 
 KERNELS = {"panel": api.FLAG_KERNEL_PANEL, "gather": api.FLAG_KERNEL_GATHER, "ring": api.FLAG_KERNEL_RING}
-RING_K = (128, 256, 512, 1024)
+RING_K = (32, 64, 128, 256, 512, 1024)
 
 
 def kernels_for(K):
@@ -50,7 +50,7 @@ def test_hand_computable(engine):
 @pytest.mark.parametrize("K", [4, 8, 12, 16, 20, 32, 36, 64, 100, 128, 192, 256, 260, 512, 1024, 2048])
 def test_every_k(engine, kernel, K):
     if kernel not in kernels_for(K):
-        pytest.skip("the ring kernel covers K = 128, 256, 512, 1024")
+        pytest.skip("the ring kernels cover K = 32, 64, 128, 256, 512, 1024")
     rng = np.random.default_rng(K)
     M, N = 257, 190
     rows, cols = random_coo(rng, M, N, 6000, empty_rows=[0, 5, 6, 7, 100, 256])
@@ -199,7 +199,7 @@ def test_benchmark_configs(engine, name, kernel):
     else:
         p = _scaled(synth.attention_mask, M=4096, half_width=64, n_global=12, K=64)
     if kernel not in kernels_for(p["K"]):
-        pytest.skip("the ring kernel covers K = 128, 256, 512, 1024")
+        pytest.skip("the ring kernels cover K = 32, 64, 128, 256, 512, 1024")
     P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], KERNELS[kernel],
                        p["panel_rows"], p["col_tile"])
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
