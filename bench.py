@@ -292,7 +292,8 @@ def main():
     handle.set_stream(stream.cuda_stream)
     kflag = {"auto": 0, "ring": api.FLAG_KERNEL_RING, "panel": api.FLAG_KERNEL_PANEL,
              "gather": api.FLAG_KERNEL_GATHER}[args.kernel]
-    kernel_name = args.kernel if args.kernel != "auto" else ("ring" if K in (32, 64, 128, 256, 512, 1024) else "panel")
+    kernel_name = args.kernel if args.kernel != "auto" else (
+        "ring" if K in (32, 64, 128, 256, 512, 1024) and nnz >= 65536 else "panel")
 
     # ---- sharding (identity at one GPU) --------------------------------------
     rows_host = rows.cpu().numpy()

@@ -398,7 +398,8 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     const uint32_t forced = flags & (SDDMM_FLAG_KERNEL_GATHER | SDDMM_FLAG_KERNEL_PANEL | SDDMM_FLAG_KERNEL_RING);
     if (forced & (forced - 1)) return SDDMM_INVALID_ARG;  // at most one kernel may be forced
     if ((flags & SDDMM_FLAG_KERNEL_RING) && !ring_supports(p->K)) return SDDMM_K_UNSUPPORTED;
-    const bool use_ring = (flags & SDDMM_FLAG_KERNEL_RING) || (!forced && ring_supports(p->K));
+    // tiny inputs are launch-bound: the panel kernel needs no counter reset and starts faster
+    const bool use_ring = (flags & SDDMM_FLAG_KERNEL_RING) || (!forced && ring_supports(p->K) && p->nnz >= 65536);
     if (use_gather && tiled_out && p->d_perm) return SDDMM_INVALID_ARG;
     CUDA_TRY(h, cudaSetDevice(h->device));
     cudaStream_t s = h->stream;

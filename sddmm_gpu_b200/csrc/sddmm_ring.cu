@@ -27,8 +27,8 @@
 // memory, L1/L2) only when the row changes -- one group ahead, right after the
 // previous group's FMAs.
 //
-// Supported: K = 128 * C with C in {1, 2, 4, 8} (K = 128 ... 1024); K = 32 and 64
-// are served by the cp.async ring of sddmm_ring_small.cu through the same launcher.
+// Used for K = 256, 512 and 1024 (C = 2, 4, 8); K = 32, 64 and 128 are served by
+// the cp.async ring of sddmm_ring_small.cu through the same launcher.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -321,9 +321,9 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
     if (nnz == 0) return cudaSuccess;
     switch (K) {
     case 32:
-    case 64:  // short rows: the cp.async ring
+    case 64:
+    case 128:  // rows up to 512 bytes: the cp.async ring (measured faster than one bulk copy per row there)
         return launch_ring_small(rows, cols, perm, sval, W, H, P, nnz, K, cols_hinted, sm_count, work_counter, stream);
-    case 128: return launch_ring_t<1>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     case 256: return launch_ring_t<2>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     case 512: return launch_ring_t<4>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     case 1024: return launch_ring_t<8>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);

@@ -1,23 +1,25 @@
-// Ring kernel for short rows (K = 32 and 64): the per-warp shared-memory ring of
+// Ring kernel for short rows (K = 32, 64 and 128): the per-warp shared-memory ring of
 // sddmm_ring.cu, filled with 16-byte asynchronous copies (cp.async) instead of
 // one bulk copy per row.
 //
-// A row of 128 or 256 bytes is too small for a bulk copy of its own (the fixed
-// cost per copy and per mbarrier phase dominates), but the reason for the ring is
+// A row of 128 to 512 bytes is too small for a bulk copy of its own (the fixed
+// cost per copy and per mbarrier phase dominates; measured on the scale-22 R-MAT
+// matrix at K = 128: 4.2 ms with these copies against 5.2 ms with one bulk copy
+// per row, while at K = 256 the bulk copies win), but the reason for the ring is
 // the same as for long rows: gathers that land in shared memory hold no registers
 // while they are in flight, so a warp can keep a whole 4 KB group (32 or 16 rows
 // of H) outstanding while it works on the previous one.  Here every lane issues
 // eight 16-byte copies per group (one warp instruction moves 512 bytes: 4 rows at
-// K = 32, 2 rows at K = 64), closes the group with cp.async.commit_group and
+// K = 32, 2 rows at K = 64, 1 row at K = 128), closes the group with cp.async.commit_group and
 // later waits for it with cp.async.wait_group -- a wait on the thread's own
 // copies only, so there is nothing that could spin for ever and no mbarrier.
 //
 // Lane sets as in the long-row kernel: the 32 lanes are B = 4096/(4K) sets of
 // LPN = 32/B lanes, one set per nonzero of the group (K = 32: every lane owns a
 // nonzero and needs no shuffle at all; K = 64: two lanes per nonzero, one
-// shuffle).  Each lane multiplies 8 float4 of its H row with its share of the W
+// shuffle; K = 128: four lanes, two shuffles).  Each lane multiplies 8 float4 of its H row with its share of the W
 // row, which stays in registers while consecutive nonzeros of the set lie in the
-// same row of S.  Rows are padded in the slot (144 / 288 bytes) so that the
+// same row of S.  Rows are padded in the slot (144 / 288 / 576 bytes) so that the
 // 128-bit shared-memory loads of a quarter-warp fall into different banks.
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -34,15 +36,14 @@ namespace {
 constexpr int SR_WARPS = 24;
 constexpr int SR_NG = 2;  // ring slots (groups) per warp
 
-template <int RB>  // row bytes: 128 (K = 32) or 256 (K = 64)
+template <int RB>  // row bytes: 128 (K = 32), 256 (K = 64) or 512 (K = 128)
 struct SmallShape {
     static constexpr int B = 4096 / RB;        // nonzeros per group: 32 / 16
     static constexpr int LPN = 32 / B;         // lanes per nonzero: 1 / 2
     static constexpr int F = RB / 16 / LPN;    // float4 per lane per row: 8
     static constexpr int PPR = RB / 16;        // 16-byte pieces per row: 8 / 16
-    static constexpr int RPI = 32 / PPR;       // rows covered by one warp-wide copy instruction: 4 / 2
-    static constexpr int NCOPY = B / RPI;      // copy instructions per group: 8
-    static constexpr int ROW_STRIDE = RB + 16 * LPN;  // 144 / 288: conflict-free 128-bit loads
+    static constexpr int NCOPY = B * PPR / 32; // copy instructions per group: 8
+    static constexpr int ROW_STRIDE = RB + (LPN < 8 ? 16 * LPN : 0);  // 144 / 288: conflict-free 128-bit loads
     static constexpr int SLOT_BYTES = (B * ROW_STRIDE + 127) / 128 * 128;
     static constexpr int K4 = RB / 16;
     static_assert(F == 8 && NCOPY == 8, "geometry");
@@ -79,8 +80,6 @@ sddmm_ring_small_kernel(const int32_t *__restrict__ rows, const int32_t *__restr
     const int64_t n_blocks = (n_groups + block_groups - 1) / block_groups;
     const char *Hb = reinterpret_cast<const char *>(H);
     const char *W_lane = reinterpret_cast<const char *>(W) + l * 16;
-    // copy role of this lane: piece `part` of row (i * RPI + crow) of the group, i = 0 .. 7
-    const int crow = lane / R::PPR, part = lane % R::PPR;
 
     float4 wc[F];     // this lane's share of the W row of its lane set's current row of S
     int wc_row = -1;
@@ -96,7 +95,8 @@ sddmm_ring_small_kernel(const int32_t *__restrict__ rows, const int32_t *__restr
         unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
 #pragma unroll
         for (int i = 0; i < R::NCOPY; ++i) {
-            const int r = i * R::RPI + crow;
+            const int piece = i * 32 + lane;  // 16-byte piece of the group handled by this lane in copy i
+            const int r = piece / R::PPR, part = piece % R::PPR;
             const unsigned cj = (unsigned)__shfl_sync(FULL, c_mine, r);
             void *dst = slot + r * R::ROW_STRIDE + part * 16;
             if (HAS_HINT)
@@ -141,7 +141,8 @@ sddmm_ring_small_kernel(const int32_t *__restrict__ rows, const int32_t *__restr
                     if (HAS_HINT) c &= 0x7fffffff;
                 }
                 // general predicated step: 8 (K = 32) or 16 (K = 64) lanes per nonzero, up to 32 / 16 nonzeros
-                const float res = warp_step<R::K4, 1, 8, false>(W, H, r, c, tail, R::K4, lane);
+                const float res = warp_step<(R::K4 < 32 ? R::K4 : 32), (R::K4 < 32 ? 1 : R::K4 / 32), (B < 8 ? B : 8), false>(
+                    W, H, r, c, tail, R::K4, lane);
                 if (lane < tail) store(off + lane, res);
             }
             continue;
@@ -243,6 +244,8 @@ cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const in
         return launch_small_t<128>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, stream);
     if (K == 64)
         return launch_small_t<256>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, stream);
+    if (K == 128)
+        return launch_small_t<512>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, stream);
     return cudaErrorInvalidValue;
 }
 
