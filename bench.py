@@ -57,6 +57,7 @@ def parse_args():
     ap.add_argument("--k", type=int, default=0, help="override K of the workload")
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (c3/c4), for quick runs")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "panel", "gather"])
+    ap.add_argument("--col-tile", type=int, default=0, help="column-tile width passed to the plan (argv[4] of the CLI)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
@@ -317,7 +318,7 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         h_bcast_ms = e0.elapsed_time(e1)
-    plan = handle.plan_coo(shard.n_rows, N, l_rows, l_cols, K, p["panel_rows"], p["col_tile"])
+    plan = handle.plan_coo(shard.n_rows, N, l_rows, l_cols, K, p["panel_rows"], args.col_tile or p["col_tile"])
     info = plan.info()
     m_nz_local = info.n_nonempty_rows
     n_nz_local = plan.count_cols()
