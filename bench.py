@@ -361,7 +361,8 @@ def main():
     traffic = ncu_traffic(p["workload"], kernel_name) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": alg_bytes,
-                "kernel_ms": kernel_ms, "kernel_ms_min": min(step_ms),
+                "kernel_ms": kernel_ms, "kernel_ms_min": min(step_ms), "kernel_ms_median": statistics.median(step_ms),
+                "frac_of_nominal_8000": achieved / 8000.0,
                 "kernel": f"sddmm_{kernel_name}_kernel"}
     if traffic:
         roofline["dram_gbs"] = traffic / (kernel_ms * 1e-3) / 1e9
@@ -460,7 +461,9 @@ def main():
                        "dense_cells": info.n_dense_cells, "dense_cell_nnz": info.n_dense_nnz,
                        "hub_columns": info.n_hub_cols},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": args.steps, "clocks": clocks.summary(),
+            # one launch per step, two when the plan split S into dense cells and a remainder
+            "gpu_launches": args.steps * (2 if (info.n_dense_cells > 0 and args.kernel == "auto") else 1),
+            "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
     plan.close()

@@ -67,30 +67,34 @@ struct RingShape {
     // that their 64-byte pieces fall into different banks
     static constexpr int ROW_STRIDE = ROW_BYTES + (LPN == 4 ? 64 : 0);
     static constexpr int SLOT_BYTES = (B * ROW_STRIDE + 127) / 128 * 128;
+    // Who issues the B row copies of a group: with four or more rows per group
+    // lanes 0..B-1 issue one copy each in the same instruction; with one or two
+    // rows lane 0 issues them one after the other (measured: K = 256 on a matrix
+    // whose H fits L2 6.5 % faster with parallel issue, K = 512 on a matrix whose
+    // H does not 4 % slower).
+    static constexpr bool PAR_ISSUE = B >= 4;
     static_assert(B >= 1 && B <= 8 && LPN * B == 32, "group geometry");
 };
 
-// B consecutive column indices, loaded as one vector by every lane (same
-// address for the whole warp).  p is aligned to min(16, 4*B) bytes.
-template <int B>
-struct ColVec {
-    int v[B];
+// The column indices a lane needs to issue a group: its own one (parallel issue),
+// or all B <= 2 of them (lane 0 issues; every lane loads the same vector).
+template <int B, bool PAR>
+struct GroupCols {
+    int v[PAR ? 1 : B];
 };
-template <int B>
-__device__ __forceinline__ ColVec<B> load_cols(const int32_t *p)
+template <int B, bool PAR>
+__device__ __forceinline__ GroupCols<B, PAR> load_group_cols(const int32_t *group, int lane)
 {
-    ColVec<B> r;
-    if constexpr (B == 1) {
-        r.v[0] = __ldcs(p);
+    GroupCols<B, PAR> r;
+    if constexpr (PAR) {
+        r.v[0] = __ldcs(group + (lane & (B - 1)));
     } else if constexpr (B == 2) {
-        const int2 t = __ldcs(reinterpret_cast<const int2 *>(p));
-        r.v[0] = t.x; r.v[1] = t.y;
+        const int2 t = __ldcs(reinterpret_cast<const int2 *>(group));
+        r.v[0] = t.x;
+        r.v[1] = t.y;
     } else {
-#pragma unroll
-        for (int i = 0; i < B / 4; ++i) {
-            const int4 t = __ldcs(reinterpret_cast<const int4 *>(p) + i);
-            r.v[4 * i] = t.x; r.v[4 * i + 1] = t.y; r.v[4 * i + 2] = t.z; r.v[4 * i + 3] = t.w;
-        }
+        static_assert(B == 1, "serial issue is for one or two rows per group");
+        r.v[0] = __ldcs(group);
     }
     return r;
 }
@@ -104,6 +108,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
 {
     using R = RingShape<C>;
     constexpr int B = R::B, LPN = R::LPN, F = R::F, NG = RING_NG;
+    constexpr bool PAR = R::PAR_ISSUE;
     constexpr int K4 = 32 * C;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -140,24 +145,32 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         pol_drop = l2_policy_evict_first();
     }
 
-    // One lane arms the slot's mbarrier with the byte count and issues the B row copies.
-    auto issue = [&](const ColVec<B> &cv) {
-        if (lane == 0) {
-            unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
-            uint64_t *bar = &bars[s_issue];
+    // Lane 0 arms the slot's mbarrier with the byte count of the whole group, then
+    // the B row copies are issued (by lanes 0..B-1 together, or by lane 0 alone).
+    // A copy that lands before the arming only drives the barrier's byte count
+    // negative for a moment: the phase cannot complete before lane 0's arrival.
+    auto copy_row = [&](unsigned char *dst, unsigned cj, uint64_t *bar) {
+        if (HAS_HINT) {
+            bulk_g2s_hint(dst, Hb + (size_t)(cj & 0x7fffffffu) * R::ROW_BYTES, R::ROW_BYTES, bar,
+                          (cj >> 31) ? pol_keep : pol_drop);
+        } else {
+            bulk_g2s(dst, Hb + (size_t)cj * R::ROW_BYTES, R::ROW_BYTES, bar);
+        }
+    };
+    auto issue = [&](const GroupCols<B, PAR> &gc) {
+        unsigned char *slot = ring + s_issue * R::SLOT_BYTES;
+        uint64_t *bar = &bars[s_issue];
+        if (lane == 0)
             asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(
                              smem_u32(bar)),
                          "r"((unsigned)(B * R::ROW_BYTES))
                          : "memory");
+        if constexpr (PAR) {
+            if (lane < B) copy_row(slot + lane * R::ROW_STRIDE, (unsigned)gc.v[0], bar);
+        } else {
+            if (lane == 0) {
 #pragma unroll
-            for (int j = 0; j < B; ++j) {
-                const unsigned cj = (unsigned)cv.v[j];
-                if (HAS_HINT) {
-                    bulk_g2s_hint(slot + j * R::ROW_STRIDE, Hb + (size_t)(cj & 0x7fffffffu) * R::ROW_BYTES, R::ROW_BYTES,
-                                  bar, (cj >> 31) ? pol_keep : pol_drop);
-                } else {
-                    bulk_g2s(slot + j * R::ROW_STRIDE, Hb + (size_t)cj * R::ROW_BYTES, R::ROW_BYTES, bar);
-                }
+                for (int j = 0; j < B; ++j) copy_row(slot + j * R::ROW_STRIDE, (unsigned)gc.v[j], bar);
             }
         }
         s_issue = (s_issue + 1 == NG) ? 0 : s_issue + 1;
@@ -210,8 +223,8 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         // prologue: NG-1 groups in flight, W of the first group, indices one step ahead
 #pragma unroll
         for (int i = 0; i < NG - 1; ++i)
-            if (i < n) issue(load_cols<B>(bcol + i * B));
-        ColVec<B> cv = load_cols<B>(bcol + clampq(NG - 1) * B);  // columns of group q + NG - 1
+            if (i < n) issue(load_group_cols<B, PAR>(bcol + i * B, lane));
+        auto cv = load_group_cols<B, PAR>(bcol + clampq(NG - 1) * B, lane);  // columns of group q + NG - 1
         {
             const int r0 = __ldcs(brow);
             if (r0 != wc_row) load_w(r0);
@@ -221,7 +234,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         for (int q = 0; q < n; ++q) {
             // keep NG-1 groups in flight: group q + NG - 1 goes into the slot freed by group q - 1
             if (q + NG - 1 < n) issue(cv);
-            cv = load_cols<B>(bcol + clampq(q + NG) * B);
+            cv = load_group_cols<B, PAR>(bcol + clampq(q + NG) * B, lane);
             const int r_fut = __ldcs(brow + clampq(q + 2) * B);
             // wait for group q
             if (!mbar_try_wait(&bars[s_cons], cons_parity) && !mbar_wait_bounded(&bars[s_cons], cons_parity)) {

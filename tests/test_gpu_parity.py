@@ -375,3 +375,21 @@ def test_bounded_wait_reports_timeout_and_handle_survives(engine):
     W = np.ones((3, 128), np.float32)
     P, _ = run_plan(engine, 3, 3, rows, cols, W, W, None, 0)
     assert np.array_equal(P, np.full(3, 128.0, np.float32))
+
+
+# ---- hub-column L2 hints (bit 31 of the plan's column copy) --------------------
+
+@pytest.mark.parametrize("K", [32, 128, 256, 1024])
+def test_hub_column_hints_do_not_change_results(engine, K, monkeypatch):
+    # force the marks on a small matrix (the default only marks when H exceeds 64 MB): results must be
+    # those of the unmarked plan bit for bit, and the oracle's within tolerance
+    p = synth.to_numpy(synth.rmat(scale=12, edge_factor=24, K=K, device="cpu"))
+    monkeypatch.setenv("SDDMM_L2_HUB_MB", "0")
+    P0, info0 = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], api.FLAG_KERNEL_RING)
+    monkeypatch.setenv("SDDMM_L2_HUB_MB", "1")
+    P1, info1 = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], api.FLAG_KERNEL_RING)
+    assert info0.n_hub_cols == 0
+    if p["N"] * K * 4 > (1 << 20):
+        assert info1.n_hub_cols > 0
+    assert np.array_equal(P0, P1)
+    assert_parity(P1, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
