@@ -384,13 +384,15 @@ def main():
             hH = torch.empty((h1 - h0, K), dtype=torch.float32, pin_memory=True).copy_(H[h0:h1])
             torch.cuda.synchronize()
 
+            staging = {}
+
             def e2e_step():
                 if world == 1:
                     plan.execute(hW, hH, hP, hS, kflag)         # H2D W, H, S; kernel; D2H P; synchronous
                 else:
-                    # every rank uploads its slice of H over its own PCIe link, slices are exchanged over NVLink
-                    multi_gpu.upload_h_sharded(H, hH, rank, world)
-                    plan.execute(hW, H, hP, hS, kflag)           # H2D of this rank's W rows and S values
+                    # every rank uploads its slice of H over its own PCIe link and the slices are exchanged
+                    # over NVLink while the rank's W rows and S values are uploaded; kernel; D2H P
+                    multi_gpu.host_step(plan, rank, world, hW, hH, H, hP, hS, kflag, staging)
 
             n_e2e = max(3, min(args.steps, 5))
             for _ in range(2):
@@ -406,14 +408,18 @@ def main():
             if world > 1:
                 dist.all_reduce(te, op=dist.ReduceOp.MAX)
             e2e_ms = float(te.item()) / n_e2e
-            h2d = 4 * (l_W.numel() + l_vals.numel() + hH.numel())
-            d2h = 4 * P.numel()
+            if world == 1:
+                h2d, d2h = plan.last_transfer_bytes()          # what the call moved (untouched W/H rows do not travel)
+            else:
+                h2d = 4 * (l_W.numel() + l_vals.numel() + hH.numel())
+                d2h = 4 * P.numel()
             tb = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(tb, op=dist.ReduceOp.SUM)
             e2e = {"value": 2.0 * nnz * K / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                    "h2d_bytes_per_step": int(tb[0].item()), "d2h_bytes_per_step": int(tb[1].item()),
-                   "ms_per_step": e2e_ms, "steps": n_e2e, "host_memory": "pinned"}
+                   "ms_per_step": e2e_ms, "steps": n_e2e, "host_memory": "pinned",
+                   "operand_bytes": 4 * (l_W.numel() + l_vals.numel() + hH.numel())}
             # the host copy of the result is the one that is checked below
             P_check = hP
         except RuntimeError as ex:  # e.g. pinned allocation refused

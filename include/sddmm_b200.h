@@ -111,7 +111,22 @@ SDDMM_API int sddmm_destroy_plan(sddmm_plan_t p);
  * (HiPC18/src/kernel.h:2-52) -- one launch, no K-slicing.
  *
  *   W, H, P : host or device pointers (detected); host buffers are copied
- *             through plan-owned device staging inside the call.
+ *             through plan-owned device staging inside the call.  With W in
+ *             host memory and a large matrix (256 MB of W or more, a million
+ *             nonzeros or more, ring-kernel K, single column tile) the call is
+ *             pipelined: H first, then W rows and S values in up to 16 chunks of
+ *             consecutive nonzeros, every chunk's kernel and the download of
+ *             its part of P running behind the uploads of the later chunks on
+ *             two internal streams; W rows that no nonzero touches between two
+ *             chunks are not uploaded.  Results are bit-identical to the
+ *             unpipelined call (SDDMM_PIPELINE=0 in the environment at
+ *             sddmm_create() switches the pipeline off).  Pinned host buffers
+ *             are needed for the copies to overlap.  In a pipelined call, W
+ *             and H buffers that are page-locked and mapped (cudaHostAlloc,
+ *             cudaHostRegister) are not copied whole: a kernel reads, over
+ *             PCIe, exactly the rows of W and H that some nonzero touches (the
+ *             reference uploads both arrays whole, sddmm.cu:71-73);
+ *             SDDMM_SPARSE_UPLOAD=0 at sddmm_create() keeps cudaMemcpy.
  *   Sval    : NULL -> the unscaled dot product, as sddmm_CPU_COO and the
  *             reference kernel store it (sddmm.cu:192, kernel.h:48);
  *             else P[i] *= Sval[i], as sddmm_CPU_CSR does (sddmm.cu:171).
@@ -123,8 +138,15 @@ SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
 
 /* Milliseconds of the kernels of the last synchronous sddmm_execute(), measured
  * with CUDA events on the compute stream -- the region the reference times and
- * prints as "Time for SDDMM with K = ..." (sddmm.cu:93,109-114). */
+ * prints as "Time for SDDMM with K = ..." (sddmm.cu:93,109-114).  For a pipelined
+ * call (see sddmm_execute) it is the span from the first chunk's kernel to the
+ * last one's, waits for the uploads in between included. */
 SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
+
+/* Bytes the last sddmm_execute() moved host -> device and device -> host (0 for
+ * operands that were already on the device).  The reference moves
+ * 4K(M+N) + 12 nnz up and 4 nnz down on every call (sddmm.cu:50-73,119). */
+SDDMM_API int sddmm_last_transfer_bytes(sddmm_plan_t p, int64_t *h2d_bytes, int64_t *d2h_bytes);
 
 /*
  * One-shot form with the shape of the reference's sddmm_GPU(S, tS, P, W, H)

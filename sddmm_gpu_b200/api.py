@@ -28,7 +28,7 @@ PLAN_DEVICE_INDICES = 0x2
 
 EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
-    "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_coo",
+    "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
@@ -76,6 +76,7 @@ def lib():
     L.sddmm_destroy_plan.argtypes = [vp]
     L.sddmm_execute.argtypes = [vp, vp, vp, vp, vp, u32]
     L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    L.sddmm_last_transfer_bytes.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.sddmm_coo.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, vp]
     L.sddmm_selftest_wait_timeout.argtypes = [vp]
     L.sddmm_plan_get_info.argtypes = [vp, C.POINTER(PlanInfo)]
@@ -202,6 +203,12 @@ class Plan:
         ms = C.c_float()
         self.handle._check(lib().sddmm_last_kernel_ms(self._p, C.byref(ms)))
         return ms.value
+
+    def last_transfer_bytes(self):
+        """(host->device, device->host) bytes moved by the last execute()."""
+        up, down = C.c_int64(0), C.c_int64(0)
+        self.handle._check(lib().sddmm_last_transfer_bytes(self._p, C.byref(up), C.byref(down)))
+        return up.value, down.value
 
     def info(self):
         inf = PlanInfo()

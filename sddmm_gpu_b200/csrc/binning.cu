@@ -249,6 +249,66 @@ cudaError_t count_distinct_cols(const int32_t *d_cols, int64_t nnz, int64_t N, i
     return cudaSuccess;
 }
 
+namespace {
+
+__global__ void row_used_flags_kernel(const int64_t *__restrict__ row_ptr, int64_t M, unsigned char *flag)
+{
+    for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < M; r += (int64_t)gridDim.x * blockDim.x)
+        flag[r] = row_ptr[r + 1] > row_ptr[r];
+}
+
+// ids of the flagged positions of [0, n), ascending, into a fresh allocation
+cudaError_t select_flagged_ids(const unsigned char *flag, int64_t n, int32_t **d_list, int64_t *n_list,
+                               cudaStream_t stream)
+{
+    *d_list = nullptr;
+    *n_list = 0;
+    if (n == 0) return cudaSuccess;
+    Scratch out;  // n ids | selected count
+    CK(out.reserve(sizeof(int32_t) * (size_t)n + 16));
+    int32_t *ids = (int32_t *)out.ptr;
+    int *d_n_sel = (int *)((char *)out.ptr + sizeof(int32_t) * (size_t)((n + 3) & ~(int64_t)3));
+    thrust::counting_iterator<int32_t> counting(0);
+    size_t tb = 0;
+    CK(cub::DeviceSelect::Flagged(nullptr, tb, counting, flag, ids, d_n_sel, (int)n, stream));
+    Scratch tmp;
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceSelect::Flagged(tmp.ptr, tb, counting, flag, ids, d_n_sel, (int)n, stream));
+    int n_sel = 0;
+    CK(cudaMemcpyAsync(&n_sel, d_n_sel, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    if (n_sel > 0) {
+        CK(cudaMalloc((void **)d_list, sizeof(int32_t) * (size_t)n_sel));
+        CK(cudaMemcpyAsync(*d_list, ids, sizeof(int32_t) * (size_t)n_sel, cudaMemcpyDeviceToDevice, stream));
+        CK(cudaStreamSynchronize(stream));
+    }
+    *n_list = n_sel;
+    return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t build_used_row_list(const int64_t *d_row_ptr, int64_t M, int32_t **d_list, int64_t *n_list,
+                                cudaStream_t stream)
+{
+    Scratch flag;
+    CK(flag.reserve((size_t)M + 16));
+    if (M > 0) row_used_flags_kernel<<<grid_for(M), TPB, 0, stream>>>(d_row_ptr, M, (unsigned char *)flag.ptr);
+    CK(cudaGetLastError());
+    return select_flagged_ids((const unsigned char *)flag.ptr, M, d_list, n_list, stream);
+}
+
+cudaError_t build_used_col_list(const int32_t *d_cols, int64_t nnz, int64_t N, int32_t **d_list, int64_t *n_list,
+                                cudaStream_t stream)
+{
+    Scratch flag;
+    CK(flag.reserve((size_t)N + 16));
+    CK(cudaMemsetAsync(flag.ptr, 0, (size_t)N + 16, stream));
+    if (nnz > 0) mark_cols_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_cols, nnz, (unsigned char *)flag.ptr);
+    CK(cudaGetLastError());
+    return select_flagged_ids((const unsigned char *)flag.ptr, N, d_list, n_list, stream);
+}
+
 cudaError_t build_tiled_order(const int32_t *d_rows, const int32_t *d_cols, int64_t nnz, int64_t N, int col_tile,
                               int32_t *d_perm, int32_t *d_rows_t, int32_t *d_cols_t, cudaStream_t stream)
 {

@@ -52,6 +52,14 @@ cudaError_t build_work_items(const int32_t *d_rows_p, const int32_t *d_cols_p, i
                              int64_t *n_items, int32_t **d_item_rows, int64_t *n_item_rows,
                              cudaStream_t stream);
 
+// Ascending list of the rows of S that hold at least one nonzero (from the row
+// pointer) or of the columns that do (from the column indices): the rows of W / H
+// that an SDDMM actually reads.  Allocates *d_list (cudaMalloc) and sets *n_list.
+cudaError_t build_used_row_list(const int64_t *d_row_ptr, int64_t M, int32_t **d_list, int64_t *n_list,
+                                cudaStream_t stream);
+cudaError_t build_used_col_list(const int32_t *d_cols, int64_t nnz, int64_t N, int32_t **d_list, int64_t *n_list,
+                                cudaStream_t stream);
+
 // Hub-column hints for the ring kernel: d_cols_hinted[j] = d_cols_p[j] with bit 31
 // set when the column is among the most popular ones whose rows of H together fit
 // budget_bytes (chosen by exact column degree, most popular first).

@@ -68,6 +68,11 @@ cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *
                          const PanelConfig &cfg, int sm_count, int *dev_status,
                          cudaStream_t stream);
 
+// Copies the listed rows (K floats each) of a row-major array in mapped, page-locked
+// host memory to the same rows of a device array; the GPU reads the host memory.
+cudaError_t launch_upload_rows(const float *mapped_host, float *dev, const int32_t *d_row_list, int64_t n_rows, int K,
+                               int n_ctas, cudaStream_t stream);
+
 // Ring kernel: H rows gathered by bulk asynchronous copies (TMA) into per-warp
 // shared-memory rings, work handed out dynamically through *work_counter (one
 // device word, zeroed by the launcher).  K must satisfy ring_supports(K)
@@ -86,7 +91,7 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream);
 
-// Ring kernel for short rows (K = 32, 64): the same per-warp rings filled with
+// Ring kernel for short rows (K = 32, 64, 128): the same per-warp rings filled with
 // 16-byte cp.async copies; reached through launch_ring.
 cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                               const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted,

@@ -10,13 +10,18 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <algorithm>
 #include <string>
+#include <vector>
 
 #include "binning.cuh"
 #include "common.cuh"
 #include "sddmm_b200.h"
 
 using namespace sddmm;
+
+// Host-operand pipeline: S is cut into at most this many chunks of consecutive nonzeros.
+#define SDDMM_PIPE_MAX_CHUNKS 16
 
 struct sddmm_handle_s {
     int device = 0;
@@ -30,6 +35,16 @@ struct sddmm_handle_s {
     int *h_status = nullptr;  // pinned mirror
     std::string last_error;
     bool dense_tensor = true;  // dense cells on the tensor cores (3xTF32); SDDMM_DENSE_TENSOR=0 selects fp32 FMA
+    // pipelined execution with host operands: compute and download streams, one
+    // "uploaded" and one "computed" event per chunk (created on first use)
+    cudaStream_t pipe_compute = nullptr, pipe_download = nullptr;
+    cudaEvent_t pipe_uploaded[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_computed[SDDMM_PIPE_MAX_CHUNKS] = {};
+    cudaEvent_t pipe_joined = nullptr;
+    bool pipeline = true;  // SDDMM_PIPELINE=0 keeps upload, kernel and download strictly one after the other
+    // pipelined calls whose host operands are page-locked and mapped upload only the rows of
+    // W and H that a nonzero touches, read by the GPU (SDDMM_SPARSE_UPLOAD=0: whole arrays by cudaMemcpy)
+    bool sparse_upload = true;
+    int upload_ctas = 0;  // CTAs of the upload kernel (SDDMM_UPLOAD_CTAS; default half the SMs)
 };
 
 struct sddmm_plan_s {
@@ -62,6 +77,18 @@ struct sddmm_plan_s {
     float *d_W = nullptr, *d_H = nullptr, *d_S = nullptr, *d_P = nullptr;
     int64_t device_bytes = 0;
     float plan_ms = 0.f, last_ms = -1.f;
+    // chunks of the host-operand pipeline (0 = not pipelined): nonzeros
+    // [pipe_nnz[i], pipe_nnz[i+1]) touch the rows pipe_row_first[i] .. pipe_row_last[i] of W
+    int n_pipe = 0;
+    int64_t pipe_nnz[SDDMM_PIPE_MAX_CHUNKS + 1] = {};
+    int32_t pipe_row_first[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_row_last[SDDMM_PIPE_MAX_CHUNKS] = {};
+    // rows of W chunk i uploads: [pipe_w_begin[i], pipe_w_end[i]) (empty when an earlier chunk brought them),
+    // = entries [pipe_list_begin[i], pipe_list_begin[i+1]) of the used-row list
+    int64_t pipe_w_begin[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_w_end[SDDMM_PIPE_MAX_CHUNKS] = {};
+    int64_t pipe_list_begin[SDDMM_PIPE_MAX_CHUNKS + 1] = {};
+    int32_t *d_used_rows = nullptr, *d_used_cols = nullptr;  // ascending ids of the rows / columns holding a nonzero
+    int64_t n_used_rows = 0, n_used_cols = 0;
+    int64_t last_h2d_bytes = 0, last_d2h_bytes = 0;  // moved by the last sddmm_execute
 };
 
 namespace {
@@ -93,6 +120,20 @@ bool is_device_ptr(const void *p)
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
+// Device-side address of a page-locked host allocation that is mapped into the
+// device's address space, or null (pageable memory, device memory, unknown).
+const float *mapped_host_ptr(const float *p)
+{
+    if (!p) return nullptr;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (a.type != cudaMemoryTypeHost || !a.devicePointer) return nullptr;
+    return static_cast<const float *>(a.devicePointer);
+}
+
 int check_k(int K)
 {
     if (K <= 0 || (K % 4) != 0 || K > SDDMM_MAX_K) return SDDMM_K_UNSUPPORTED;
@@ -122,10 +163,26 @@ void free_plan_memory(sddmm_plan_s *p)
     p->dense.release();
     cudaFree(p->d_items_s);
     cudaFree(p->d_item_rows_s);
+    cudaFree(p->d_used_rows);
+    cudaFree(p->d_used_cols);
     cudaFree(p->d_W);
     cudaFree(p->d_H);
     cudaFree(p->d_S);
     cudaFree(p->d_P);
+}
+
+// Streams and events of the host-operand pipeline, created on first use.
+cudaError_t ensure_pipeline(sddmm_handle_s *h)
+{
+    if (h->pipe_joined) return cudaSuccess;
+    cudaError_t e = cudaStreamCreateWithFlags(&h->pipe_compute, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->pipe_download, cudaStreamNonBlocking);
+    for (int i = 0; i < SDDMM_PIPE_MAX_CHUNKS && e == cudaSuccess; ++i) {
+        e = cudaEventCreateWithFlags(&h->pipe_uploaded[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_computed[i], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_joined, cudaEventDisableTiming);
+    return e;
 }
 
 // After a synchronising point: turn the device status word into a status code.
@@ -202,6 +259,13 @@ int sddmm_create(sddmm_handle_t *out, int device)
     *h->h_status = DEV_OK;
     h->stream = h->own_stream;
     if (const char *env = std::getenv("SDDMM_DENSE_TENSOR")) h->dense_tensor = std::atoi(env) != 0;
+    if (const char *env = std::getenv("SDDMM_PIPELINE")) h->pipeline = std::atoi(env) != 0;
+    if (const char *env = std::getenv("SDDMM_SPARSE_UPLOAD")) h->sparse_upload = std::atoi(env) != 0;
+    h->upload_ctas = h->sm_count / 2 > 0 ? h->sm_count / 2 : 1;
+    if (const char *env = std::getenv("SDDMM_UPLOAD_CTAS")) {
+        const int v = std::atoi(env);
+        if (v > 0 && v <= 4096) h->upload_ctas = v;
+    }
     *out = h;
     return SDDMM_OK;
 }
@@ -216,6 +280,11 @@ int sddmm_destroy(sddmm_handle_t h)
     if (h->d_status) cudaFree(h->d_status);
     if (h->d_work_counter) cudaFree(h->d_work_counter);
     if (h->h_status) cudaFreeHost(h->h_status);
+    if (h->pipe_compute) cudaStreamDestroy(h->pipe_compute);
+    if (h->pipe_download) cudaStreamDestroy(h->pipe_download);
+    for (cudaEvent_t e : h->pipe_uploaded) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->pipe_computed) if (e) cudaEventDestroy(e);
+    if (h->pipe_joined) cudaEventDestroy(h->pipe_joined);
     (void)cudaGetLastError();
     delete h;
     return SDDMM_OK;
@@ -366,6 +435,43 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
                                             &p->n_hub_cols, &thr, s));
         }
     }
+    // Host-operand pipeline (sddmm_execute with W in host memory): cut S into chunks
+    // of consecutive nonzeros, about 128 MB of W rows each, and note the first and
+    // last row of every chunk -- rows are sorted, so a chunk needs one contiguous
+    // block of W rows, and W rows between two chunks that no nonzero touches are
+    // never uploaded.
+    if (ring_supports(K) && p->n_col_tiles == 1 && p->dense.n_cells == 0 && nnz >= (1 << 20)) {
+        int64_t chunks = (int64_t)sizeof(float) * M * K / (128ll << 20);
+        if (chunks > SDDMM_PIPE_MAX_CHUNKS) chunks = SDDMM_PIPE_MAX_CHUNKS;
+        if (chunks >= 2) {
+            for (int i = 0; i < chunks; ++i) p->pipe_nnz[i] = (nnz * i / chunks) & ~(int64_t)31;
+            p->pipe_nnz[chunks] = nnz;
+            for (int i = 0; i < chunks; ++i) {
+                PLAN_TRY(cudaMemcpyAsync(&p->pipe_row_first[i], p->d_rows + p->pipe_nnz[i], sizeof(int32_t),
+                                         cudaMemcpyDeviceToHost, s));
+                PLAN_TRY(cudaMemcpyAsync(&p->pipe_row_last[i], p->d_rows + p->pipe_nnz[i + 1] - 1, sizeof(int32_t),
+                                         cudaMemcpyDeviceToHost, s));
+            }
+            p->n_pipe = (int)chunks;
+            // the rows of W and H that are read at all, for the row upload from mapped host memory
+            PLAN_TRY(build_used_row_list(p->d_row_ptr, M, &p->d_used_rows, &p->n_used_rows, s));
+            PLAN_TRY(build_used_col_list(p->d_cols, nnz, N, &p->d_used_cols, &p->n_used_cols, s));
+            p->device_bytes += (int64_t)sizeof(int32_t) * (p->n_used_rows + p->n_used_cols);
+            std::vector<int32_t> used((size_t)p->n_used_rows);
+            PLAN_TRY(cudaMemcpyAsync(used.data(), p->d_used_rows, sizeof(int32_t) * used.size(), cudaMemcpyDeviceToHost, s));
+            PLAN_TRY(cudaStreamSynchronize(s));  // also completes the copies of the chunks' first and last rows
+            int64_t next_row = 0;  // first row of W no earlier chunk uploads
+            for (int i = 0; i < chunks; ++i) {
+                const int64_t r0 = p->pipe_row_first[i] > next_row ? p->pipe_row_first[i] : next_row;
+                const int64_t r1 = (int64_t)p->pipe_row_last[i] + 1;
+                p->pipe_w_begin[i] = r0;
+                p->pipe_w_end[i] = r1 > r0 ? r1 : r0;
+                p->pipe_list_begin[i] = std::lower_bound(used.begin(), used.end(), (int32_t)r0) - used.begin();
+                if (r1 > next_row) next_row = r1;
+            }
+            p->pipe_list_begin[chunks] = (int64_t)used.size();
+        }
+    }
     PLAN_TRY(cudaEventRecord(t1, s));
     PLAN_TRY(cudaEventSynchronize(t1));
     PLAN_TRY(cudaEventElapsedTime(&p->plan_ms, t0, t1));
@@ -413,30 +519,89 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     float *dP = P;
     const size_t wbytes = sizeof(float) * (size_t)p->M * p->K, hbytes = sizeof(float) * (size_t)p->N * p->K;
     const size_t nbytes = sizeof(float) * (size_t)p->nnz;
+    // W in host memory and a plain ring-kernel plan: upload W (and S) chunk by chunk
+    // and let every chunk's kernel and download run behind the later uploads
+    const bool pipelined = h->pipeline && p->n_pipe > 0 && !w_dev && use_ring && !tiled_out && !p->d_perm &&
+                           p->dense.n_cells == 0;
+    // page-locked, mapped host arrays are read row by row by the GPU: only the rows a nonzero touches travel
+    const float *W_mapped = (pipelined && h->sparse_upload) ? mapped_host_ptr(W) : nullptr;
+    const float *H_mapped = (pipelined && h->sparse_upload && !h_dev) ? mapped_host_ptr(H) : nullptr;
+    p->last_h2d_bytes = p->last_d2h_bytes = 0;
     if (!h_dev) {
         if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
-        CUDA_TRY(h, cudaMemcpyAsync(p->d_H, H, hbytes, cudaMemcpyHostToDevice, s));
+        if (H_mapped) {
+            CUDA_TRY(h, launch_upload_rows(H_mapped, p->d_H, p->d_used_cols, p->n_used_cols, p->K, h->upload_ctas, s));
+            p->last_h2d_bytes += (int64_t)sizeof(float) * p->n_used_cols * p->K;
+        } else {
+            CUDA_TRY(h, cudaMemcpyAsync(p->d_H, H, hbytes, cudaMemcpyHostToDevice, s));
+            p->last_h2d_bytes += (int64_t)hbytes;
+        }
         dH = p->d_H;
     }
     if (!w_dev) {
         if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
-        CUDA_TRY(h, cudaMemcpyAsync(p->d_W, W, wbytes, cudaMemcpyHostToDevice, s));
+        if (!pipelined) {
+            CUDA_TRY(h, cudaMemcpyAsync(p->d_W, W, wbytes, cudaMemcpyHostToDevice, s));
+            p->last_h2d_bytes += (int64_t)wbytes;
+        }
         dW = p->d_W;
     }
     if (Sval && !s_dev) {
         if (!p->d_S) CUDA_TRY(h, dev_alloc(p, &p->d_S, (size_t)p->nnz));
-        CUDA_TRY(h, cudaMemcpyAsync(p->d_S, Sval, nbytes, cudaMemcpyHostToDevice, s));
+        if (!pipelined) CUDA_TRY(h, cudaMemcpyAsync(p->d_S, Sval, nbytes, cudaMemcpyHostToDevice, s));
+        p->last_h2d_bytes += (int64_t)nbytes;
         dS = p->d_S;
     }
     if (!p_dev) {
         if (!p->d_P) CUDA_TRY(h, dev_alloc(p, &p->d_P, (size_t)p->nnz));
         dP = p->d_P;
+        p->last_d2h_bytes = (int64_t)nbytes;
     }
 
     // every kernel moves 16-byte vectors
     if ((((uintptr_t)dW | (uintptr_t)dH) & 15u) != 0) {
         h->last_error = "W and H must be 16-byte aligned on the device";
         return SDDMM_INVALID_ARG;
+    }
+    if (pipelined) {
+        CUDA_TRY(h, ensure_pipeline(h));
+        const int32_t *cols_p = p->d_cols_hint ? p->d_cols_hint : p->d_cols;
+        for (int i = 0; i < p->n_pipe; ++i) {
+            const int64_t n0 = p->pipe_nnz[i], cnt = p->pipe_nnz[i + 1] - n0;
+            const int64_t r0 = p->pipe_w_begin[i], r1 = p->pipe_w_end[i];
+            if (W_mapped) {
+                const int64_t l0 = p->pipe_list_begin[i], ln = p->pipe_list_begin[i + 1] - l0;
+                CUDA_TRY(h, launch_upload_rows(W_mapped, p->d_W, p->d_used_rows + l0, ln, p->K, h->upload_ctas, s));
+                p->last_h2d_bytes += (int64_t)sizeof(float) * ln * p->K;
+            } else if (r1 > r0) {
+                CUDA_TRY(h, cudaMemcpyAsync(p->d_W + r0 * p->K, W + r0 * p->K, sizeof(float) * (size_t)(r1 - r0) * p->K,
+                                            cudaMemcpyHostToDevice, s));
+                p->last_h2d_bytes += (int64_t)sizeof(float) * (r1 - r0) * p->K;
+            }
+            if (Sval && !s_dev)
+                CUDA_TRY(h, cudaMemcpyAsync(p->d_S + n0, Sval + n0, sizeof(float) * (size_t)cnt, cudaMemcpyHostToDevice, s));
+            CUDA_TRY(h, cudaEventRecord(h->pipe_uploaded[i], s));
+            CUDA_TRY(h, cudaStreamWaitEvent(h->pipe_compute, h->pipe_uploaded[i], 0));
+            if (i == 0) CUDA_TRY(h, cudaEventRecord(h->ev0, h->pipe_compute));
+            CUDA_TRY(h, launch_ring(p->d_rows + n0, cols_p + n0, nullptr, dS ? dS + n0 : nullptr, dW, dH, dP + n0, cnt, p->K,
+                                    p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status,
+                                    h->pipe_compute));
+            CUDA_TRY(h, cudaEventRecord(h->pipe_computed[i], h->pipe_compute));
+            if (!p_dev) {
+                CUDA_TRY(h, cudaStreamWaitEvent(h->pipe_download, h->pipe_computed[i], 0));
+                CUDA_TRY(h, cudaMemcpyAsync(P + n0, dP + n0, sizeof(float) * (size_t)cnt, cudaMemcpyDeviceToHost,
+                                            h->pipe_download));
+            }
+        }
+        CUDA_TRY(h, cudaEventRecord(h->ev1, h->pipe_compute));
+        // the caller's stream continues only after the last kernel and the last download
+        cudaStream_t last = p_dev ? h->pipe_compute : h->pipe_download;
+        CUDA_TRY(h, cudaEventRecord(h->pipe_joined, last));
+        CUDA_TRY(h, cudaStreamWaitEvent(s, h->pipe_joined, 0));
+        CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(h, cudaStreamSynchronize(s));
+        CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
+        return check_device_status(h);
     }
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (!forced && !tiled_out && p->dense.n_cells > 0) {
@@ -484,6 +649,14 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     CUDA_TRY(h, cudaStreamSynchronize(s));
     CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
     return check_device_status(h);
+}
+
+int sddmm_last_transfer_bytes(sddmm_plan_t p, int64_t *h2d_bytes, int64_t *d2h_bytes)
+{
+    if (!p) return SDDMM_INVALID_ARG;
+    if (h2d_bytes) *h2d_bytes = p->last_h2d_bytes;
+    if (d2h_bytes) *d2h_bytes = p->last_d2h_bytes;
+    return SDDMM_OK;
 }
 
 int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms)

@@ -65,19 +65,30 @@ def broadcast_h(H, src=0, group=None, chunks=1):
     return handles
 
 
-def upload_h_sharded(H_dev, H_host_slice, rank, world, group=None):
-    """Bring a host-resident H into every rank's device memory using all PCIe links:
-    rank r copies rows [r*n/world, (r+1)*n/world) of H from its pinned host slice to
-    its GPU, then the slices are exchanged over NVLink (one broadcast per slice, into
-    each GPU's own copy of H).  Returns nothing; H_dev is complete on return of the
-    collectives (stream-ordered)."""
+def exchange_h_slices(H_dev, rank, world, group=None):
+    """Every rank holds rows [r*n/world, (r+1)*n/world) of H in its own copy H_dev;
+    afterwards every copy is complete.  One all-gather (in place) when the slices have
+    equal length, one broadcast per slice otherwise.  NVLink / NVSwitch traffic only."""
+    if world == 1:
+        return
     n = H_dev.shape[0]
     bounds = [(n * r) // world for r in range(world + 1)]
-    H_dev[bounds[rank]:bounds[rank + 1]].copy_(H_host_slice, non_blocking=True)
-    if world > 1:
-        for r in range(world):
-            if bounds[r + 1] > bounds[r]:
-                dist.broadcast(H_dev[bounds[r]:bounds[r + 1]], src=r, group=group)
+    if n % world == 0:
+        dist.all_gather_into_tensor(H_dev, H_dev[bounds[rank]:bounds[rank + 1]], group=group)
+        return
+    for r in range(world):
+        if bounds[r + 1] > bounds[r]:
+            dist.broadcast(H_dev[bounds[r]:bounds[r + 1]], src=r, group=group)
+
+
+def upload_h_sharded(H_dev, H_host_slice, rank, world, group=None):
+    """Bring a host-resident H into every rank's device memory using all PCIe links:
+    rank r copies its slice of H's rows from its pinned host memory to its GPU, then the
+    slices are exchanged (exchange_h_slices).  H_dev is complete on return of the
+    collectives (stream-ordered)."""
+    a, b = h_slice_bounds(H_dev.shape[0], rank, world)
+    H_dev[a:b].copy_(H_host_slice, non_blocking=True)
+    exchange_h_slices(H_dev, rank, world, group)
 
 
 def h_slice_bounds(n, rank, world):
@@ -102,6 +113,40 @@ def gather_p(P_local, shard, group=None):
     return out
 
 
+def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0, staging=None):
+    """One SDDMM on this rank's row block with every operand in (pinned) host memory:
+    this rank's rows of W, its 1/world slice of H's rows, its S values; P comes back to
+    host memory.  Order on the rank's PCIe link: the H slice first, then W rows and S
+    values (on a side stream) while the H slices are exchanged over NVLink on the current
+    stream (which must be the stream the plan's handle launches on); the kernel starts
+    when both are in place.  `staging` (a dict the caller keeps) holds the device copies
+    of W and S and the side stream between calls."""
+    staging = staging if staging is not None else {}
+    cur = torch.cuda.current_stream()
+    side = staging.get("side")
+    if side is None:
+        side = staging["side"] = torch.cuda.Stream()
+    a, b = h_slice_bounds(H_dev.shape[0], rank, world)
+    H_dev[a:b].copy_(H_host_slice, non_blocking=True)
+    slice_up = torch.cuda.Event()
+    slice_up.record(cur)
+
+    def staged(name, host):
+        t = staging.get(name)
+        if t is None or t.shape != host.shape:
+            t = staging[name] = torch.empty(host.shape, dtype=host.dtype, device=H_dev.device)
+        t.copy_(host, non_blocking=True)
+        return t
+
+    side.wait_event(slice_up)
+    with torch.cuda.stream(side):
+        W_dev = staged("W", W_host)
+        S_dev = staged("S", Sval_host) if Sval_host is not None else None
+    exchange_h_slices(H_dev, rank, world)
+    cur.wait_stream(side)
+    plan.execute(W_dev, H_dev, P_host, S_dev, flags)   # kernel and download of P; synchronous
+
+
 class ShardedSddmm:
     """One rank's plan over its row block.  execute() takes this rank's W rows,
     the full (already broadcast) H and returns this rank's slice of P."""
@@ -123,6 +168,13 @@ class ShardedSddmm:
 
     def execute(self, W_local, H, P_local, Sval_local=None, flags=0):
         self.plan.execute(W_local, H, P_local, Sval_local, flags)
+
+    def execute_from_host(self, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0):
+        """execute() with every operand in pinned host memory (see host_step)."""
+        if not hasattr(self, "_staging"):
+            self._staging = {}
+        host_step(self.plan, self.shard.rank, self.shard.world, W_host, H_host_slice, H_dev, P_host, Sval_host,
+                  flags, self._staging)
 
     def close(self):
         self.plan.close()

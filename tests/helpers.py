@@ -28,12 +28,13 @@ def assert_parity(P_gpu, rows, cols, W, H, vals=None, tol=REL_TOL):
     _, A = oracle.cpu.sddmm_coo_f64(rows, cols, W, H, vals)
     P_gpu = np.asarray(P_gpu, dtype=np.float64)
     ref64 = ref.astype(np.float64)
+    assert np.isfinite(P_gpu).all(), f"{(~np.isfinite(P_gpu)).sum()} results are not finite (unwritten or NaN)"
     err = np.abs(P_gpu - ref64)
     bound = tol * np.maximum(np.abs(ref64), A)
     bad = np.nonzero(err > bound)[0]
     assert bad.size == 0, (f"{bad.size} of {ref.size} nonzeros out of tolerance; first {bad[:5]}: "
                            f"gpu {P_gpu[bad[:5]]} ref {ref64[bad[:5]]}")
-    well = np.abs(ref64) >= 1e-2 * A
+    well = (np.abs(ref64) >= 1e-2 * A) & (np.abs(ref64) > 0)   # an exactly zero S value gives ref = A = 0
     if well.any():
         rel = err[well] / np.abs(ref64[well])
         assert rel.max() <= tol, f"max relative error {rel.max()} on well-conditioned nonzeros"

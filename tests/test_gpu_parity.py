@@ -393,3 +393,50 @@ def test_hub_column_hints_do_not_change_results(engine, K, monkeypatch):
         assert info1.n_hub_cols > 0
     assert np.array_equal(P0, P1)
     assert_parity(P1, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+
+
+# ---- host operands: pipelined upload / compute / download ----------------------
+
+def test_host_operand_pipeline_matches_unpipelined(monkeypatch):
+    # 256 MB of W triggers the chunked pipeline of sddmm_execute with host operands;
+    # its result must equal the one-shot path bit for bit and the oracle within tolerance
+    p = synth.to_numpy(synth.rmat(scale=18, edge_factor=6, K=256, device="cpu"))
+    outs = []
+    for pipeline in ("1", "0"):
+        monkeypatch.setenv("SDDMM_PIPELINE", pipeline)
+        h = api.Handle(0)
+        P, _ = run_plan(h, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+        P_unscaled, _ = run_plan(h, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], None)
+        h.close()
+        outs.append((P, P_unscaled))
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+    assert_parity(outs[0][0], p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+
+
+def test_pinned_host_operands_upload_only_touched_rows(monkeypatch):
+    # page-locked W and H: the pipelined call reads just the rows a nonzero touches; the result must be the
+    # pageable-memory result bit for bit, and the byte count must be the touched rows' (plus S)
+    import torch
+    p = synth.to_numpy(synth.rmat(scale=18, edge_factor=6, K=256, device="cpu"))
+    K, nnz = 256, p["rows"].shape[0]
+    h = api.Handle(0)
+    plan = h.plan_coo(p["M"], p["N"], p["rows"], p["cols"], K)
+    P_pageable = np.full(nnz, np.nan, np.float32)
+    plan.execute(p["W"], p["H"], P_pageable, p["vals"])
+    up_pageable, down = plan.last_transfer_bytes()
+    Wp = torch.from_numpy(p["W"]).pin_memory()
+    Hp = torch.from_numpy(p["H"]).pin_memory()
+    Sp = torch.from_numpy(p["vals"]).pin_memory()
+    Pp = torch.full((nnz,), float("nan")).pin_memory()
+    plan.execute(Wp, Hp, Pp, Sp)
+    up_pinned, down2 = plan.last_transfer_bytes()
+    info = plan.info()
+    n_cols = plan.count_cols()
+    plan.close()
+    h.close()
+    assert down == down2 == 4 * nnz
+    assert up_pinned == 4 * K * (info.n_nonempty_rows + n_cols) + 4 * nnz
+    assert up_pinned < up_pageable <= 4 * K * (p["M"] + p["N"]) + 4 * nnz
+    assert np.array_equal(Pp.numpy(), P_pageable)
+    assert_parity(P_pageable, p["rows"], p["cols"], p["W"], p["H"], p["vals"])

@@ -82,3 +82,25 @@ def test_shards_cover_the_matrix_without_overlap():
         for s in shards:
             lr, lc = multi_gpu.local_pattern(s, rows, cols)
             assert lr.shape[0] == s.nnz and (s.nnz == 0 or (lr.min() >= 0 and lr.max() < s.n_rows))
+
+
+def _h_exchange_worker(rank, world, port, n_rows):
+    sys.path.insert(0, ROOT)
+    from sddmm_gpu_b200 import multi_gpu
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    K = 12
+    H = torch.arange(n_rows * K, dtype=torch.float32).reshape(n_rows, K)
+    a, b = multi_gpu.h_slice_bounds(n_rows, rank, world)
+    H_mine = torch.full_like(H, -1.0)            # nothing but this rank's slice is known beforehand
+    multi_gpu.upload_h_sharded(H_mine, H[a:b].clone(), rank, world)
+    assert torch.equal(H_mine, H), f"rank {rank}: H not assembled"
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_h_slices_are_assembled_on_every_rank():
+    # equal slices take the all-gather, ragged ones a broadcast per slice
+    for n_rows in (64, 61):
+        mp.spawn(_h_exchange_worker, args=(2, _free_port(), n_rows), nprocs=2, join=True)
