@@ -385,6 +385,9 @@ def main():
             torch.cuda.synchronize()
 
             staging = {}
+            up_bytes = [0]
+            h_rows = multi_gpu.used_h_rows_of_slice(cols, N, rank, world) if world > 1 else None
+            torch.cuda.synchronize()
 
             def e2e_step():
                 if world == 1:
@@ -392,7 +395,7 @@ def main():
                 else:
                     # every rank uploads its slice of H over its own PCIe link and the slices are exchanged
                     # over NVLink while the rank's W rows and S values are uploaded; kernel; D2H P
-                    multi_gpu.host_step(plan, rank, world, hW, hH, H, hP, hS, kflag, staging)
+                    up_bytes[0] = multi_gpu.host_step(plan, rank, world, hW, hH, H, hP, hS, kflag, staging, h_rows)
 
             n_e2e = max(3, min(args.steps, 5))
             for _ in range(2):
@@ -411,15 +414,16 @@ def main():
             if world == 1:
                 h2d, d2h = plan.last_transfer_bytes()          # what the call moved (untouched W/H rows do not travel)
             else:
-                h2d = 4 * (l_W.numel() + l_vals.numel() + hH.numel())
+                h2d = up_bytes[0]
                 d2h = 4 * P.numel()
-            tb = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
+            operand = 4 * (l_W.numel() + l_vals.numel() + hH.numel())
+            tb = torch.tensor([h2d, d2h, operand], device=device, dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(tb, op=dist.ReduceOp.SUM)
             e2e = {"value": 2.0 * nnz * K / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                    "h2d_bytes_per_step": int(tb[0].item()), "d2h_bytes_per_step": int(tb[1].item()),
                    "ms_per_step": e2e_ms, "steps": n_e2e, "host_memory": "pinned",
-                   "operand_bytes": 4 * (l_W.numel() + l_vals.numel() + hH.numel())}
+                   "operand_bytes": int(tb[2].item())}
             # the host copy of the result is the one that is checked below
             P_check = hP
         except RuntimeError as ex:  # e.g. pinned allocation refused

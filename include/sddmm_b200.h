@@ -143,6 +143,29 @@ SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
  * last one's, waits for the uploads in between included. */
 SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
 
+/*
+ * The rows of W (which = 0) or of H (which = 1) that an SDDMM over this plan
+ * reads: ascending ids of the rows / columns of S that hold at least one
+ * nonzero, as a device array owned by the plan (valid until the plan is
+ * destroyed), built on first request.  Together with sddmm_upload_rows this
+ * replaces the whole-array uploads of sddmm_GPU (HiPC18/src/sddmm.cu:71-73) for
+ * callers that stage the operands themselves (e.g. one process per GPU).
+ */
+SDDMM_API int sddmm_plan_used_lines(sddmm_plan_t p, int which, const int32_t **d_ids, int64_t *n);
+
+/*
+ * Copy the listed rows of a row-major fp32 array with K columns from
+ * page-locked, mapped host memory (cudaHostAlloc / cudaHostRegister) to the same
+ * rows of a device array; a kernel reads the host rows over PCIe, so rows that
+ * are not listed do not travel.  Stream-ordered on cuda_stream (a cudaStream_t
+ * as void*; NULL = the handle's stream); returns after enqueueing.
+ * SDDMM_INVALID_ARG when `host` is not mapped page-locked memory (nothing is
+ * launched).  Counterpart in the reference: the cudaMemcpy of W and H
+ * (sddmm.cu:71-73).
+ */
+SDDMM_API int sddmm_upload_rows(sddmm_handle_t h, const float *host, float *dev, const int32_t *d_row_ids,
+                                int64_t n_rows, int K, void *cuda_stream);
+
 /* Bytes the last sddmm_execute() moved host -> device and device -> host (0 for
  * operands that were already on the device).  The reference moves
  * 4K(M+N) + 12 nnz up and 4 nnz down on every call (sddmm.cu:50-73,119). */

@@ -28,7 +28,7 @@ PLAN_DEVICE_INDICES = 0x2
 
 EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
-    "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_coo",
+    "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
@@ -77,6 +77,8 @@ def lib():
     L.sddmm_execute.argtypes = [vp, vp, vp, vp, vp, u32]
     L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
     L.sddmm_last_transfer_bytes.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
+    L.sddmm_plan_used_lines.argtypes = [vp, C.c_int, C.POINTER(vp), C.POINTER(i64)]
+    L.sddmm_upload_rows.argtypes = [vp, vp, vp, vp, i64, C.c_int, vp]
     L.sddmm_coo.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, vp]
     L.sddmm_selftest_wait_timeout.argtypes = [vp]
     L.sddmm_plan_get_info.argtypes = [vp, C.POINTER(PlanInfo)]
@@ -155,6 +157,12 @@ class Handle:
         """cuda_stream: integer cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream) or None."""
         self._check(lib().sddmm_set_stream(self._h, cuda_stream))
 
+    def upload_rows(self, host, dev, d_row_ids, n_rows, K, cuda_stream=None):
+        """Copy the listed rows of a pinned host array to the same rows of a device array (the GPU
+        reads the host rows); `d_row_ids` is a device int32 tensor or a device address."""
+        self._check(lib().sddmm_upload_rows(self._h, _ptr(host), _ptr(dev), _ptr(d_row_ids), n_rows, K,
+                                            cuda_stream))
+
     def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, col_tile_hint=0, flags=0, nnz=None):
         if nnz is None:
             nnz = int(rows.shape[0])
@@ -203,6 +211,13 @@ class Plan:
         ms = C.c_float()
         self.handle._check(lib().sddmm_last_kernel_ms(self._p, C.byref(ms)))
         return ms.value
+
+    def used_lines(self, which):
+        """(device address, count) of the plan's list of rows (which=0) / columns (which=1) of S
+        that hold a nonzero: the rows of W / H the SDDMM reads.  Owned by the plan."""
+        ptr, n = C.c_void_p(), C.c_int64(0)
+        self.handle._check(lib().sddmm_plan_used_lines(self._p, which, C.byref(ptr), C.byref(n)))
+        return ptr.value or 0, n.value
 
     def last_transfer_bytes(self):
         """(host->device, device->host) bytes moved by the last execute()."""

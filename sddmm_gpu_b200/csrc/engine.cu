@@ -651,6 +651,55 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     return check_device_status(h);
 }
 
+int sddmm_plan_used_lines(sddmm_plan_t p, int which, const int32_t **d_ids, int64_t *n)
+{
+    if (!p || !d_ids || !n || (which != 0 && which != 1)) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    *d_ids = nullptr;
+    *n = 0;
+    if (p->nnz == 0) return SDDMM_OK;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    if (which == 0) {
+        if (!p->d_used_rows) {
+            CUDA_TRY(h, build_used_row_list(p->d_row_ptr, p->M, &p->d_used_rows, &p->n_used_rows, h->stream));
+            p->device_bytes += (int64_t)sizeof(int32_t) * p->n_used_rows;
+        }
+        *d_ids = p->d_used_rows;
+        *n = p->n_used_rows;
+    } else {
+        if (!p->d_used_cols) {
+            CUDA_TRY(h, build_used_col_list(p->d_cols, p->nnz, p->N, &p->d_used_cols, &p->n_used_cols, h->stream));
+            p->device_bytes += (int64_t)sizeof(int32_t) * p->n_used_cols;
+        }
+        *d_ids = p->d_used_cols;
+        *n = p->n_used_cols;
+    }
+    return SDDMM_OK;
+}
+
+int sddmm_upload_rows(sddmm_handle_t h, const float *host, float *dev, const int32_t *d_row_ids, int64_t n_rows, int K,
+                      void *cuda_stream)
+{
+    if (!h || n_rows < 0) return SDDMM_INVALID_ARG;
+    int st = check_k(K);
+    if (st != SDDMM_OK) return st;
+    if (n_rows == 0) return SDDMM_OK;
+    if (!host || !dev || !d_row_ids) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    const float *mapped = mapped_host_ptr(host);
+    if (!mapped) {
+        h->last_error = "sddmm_upload_rows needs page-locked, mapped host memory (cudaHostAlloc / cudaHostRegister)";
+        return SDDMM_INVALID_ARG;
+    }
+    if (!is_device_ptr(dev) || !is_device_ptr(d_row_ids) || (((uintptr_t)mapped | (uintptr_t)dev) & 15u) != 0) {
+        h->last_error = "sddmm_upload_rows: dev and d_row_ids must be device memory, both arrays 16-byte aligned";
+        return SDDMM_INVALID_ARG;
+    }
+    CUDA_TRY(h, launch_upload_rows(mapped, dev, d_row_ids, n_rows, K, h->upload_ctas,
+                                   cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    return SDDMM_OK;
+}
+
 int sddmm_last_transfer_bytes(sddmm_plan_t p, int64_t *h2d_bytes, int64_t *d2h_bytes)
 {
     if (!p) return SDDMM_INVALID_ARG;

@@ -113,21 +113,38 @@ def gather_p(P_local, shard, group=None):
     return out
 
 
-def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0, staging=None):
+def used_h_rows_of_slice(cols_all, N, rank, world):
+    """Ids, relative to this rank's slice of H's rows, of the H rows that any nonzero of
+    the WHOLE matrix touches (`cols_all`: every column index of S, a device tensor): the
+    rows of the slice worth uploading.  int32 device tensor, ascending."""
+    a, b = h_slice_bounds(N, rank, world)
+    used = torch.zeros(N, dtype=torch.bool, device=cols_all.device)
+    used[cols_all.long()] = True
+    return (torch.nonzero(used[a:b]).squeeze(1)).to(torch.int32).contiguous()
+
+
+def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0, staging=None,
+              h_slice_rows=None):
     """One SDDMM on this rank's row block with every operand in (pinned) host memory:
     this rank's rows of W, its 1/world slice of H's rows, its S values; P comes back to
     host memory.  Order on the rank's PCIe link: the H slice first, then W rows and S
     values (on a side stream) while the H slices are exchanged over NVLink on the current
     stream (which must be the stream the plan's handle launches on); the kernel starts
-    when both are in place.  `staging` (a dict the caller keeps) holds the device copies
-    of W and S and the side stream between calls."""
+    when both are in place.  Only rows that a nonzero touches travel over PCIe: the rows
+    of W from the plan's own list, the rows of the H slice from `h_slice_rows`
+    (used_h_rows_of_slice; None uploads the whole slice).  `staging` (a dict the caller
+    keeps) holds the device copies of W and S and the side stream between calls."""
     staging = staging if staging is not None else {}
+    handle, K = plan.handle, H_dev.shape[1]
     cur = torch.cuda.current_stream()
     side = staging.get("side")
     if side is None:
         side = staging["side"] = torch.cuda.Stream()
     a, b = h_slice_bounds(H_dev.shape[0], rank, world)
-    H_dev[a:b].copy_(H_host_slice, non_blocking=True)
+    if h_slice_rows is not None:
+        handle.upload_rows(H_host_slice, H_dev[a:b], h_slice_rows, h_slice_rows.numel(), K, cur.cuda_stream)
+    else:
+        H_dev[a:b].copy_(H_host_slice, non_blocking=True)
     slice_up = torch.cuda.Event()
     slice_up.record(cur)
 
@@ -135,16 +152,22 @@ def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=
         t = staging.get(name)
         if t is None or t.shape != host.shape:
             t = staging[name] = torch.empty(host.shape, dtype=host.dtype, device=H_dev.device)
-        t.copy_(host, non_blocking=True)
         return t
 
     side.wait_event(slice_up)
     with torch.cuda.stream(side):
         W_dev = staged("W", W_host)
-        S_dev = staged("S", Sval_host) if Sval_host is not None else None
+        ids, n_ids = plan.used_lines(0)
+        handle.upload_rows(W_host, W_dev, ids, n_ids, K, side.cuda_stream)
+        S_dev = None
+        if Sval_host is not None:
+            S_dev = staged("S", Sval_host)
+            S_dev.copy_(Sval_host, non_blocking=True)
     exchange_h_slices(H_dev, rank, world)
     cur.wait_stream(side)
     plan.execute(W_dev, H_dev, P_host, S_dev, flags)   # kernel and download of P; synchronous
+    n_h = h_slice_rows.numel() if h_slice_rows is not None else (b - a)
+    return 4 * K * (n_ids + n_h) + (4 * Sval_host.numel() if Sval_host is not None else 0)   # bytes uploaded
 
 
 class ShardedSddmm:
@@ -169,12 +192,12 @@ class ShardedSddmm:
     def execute(self, W_local, H, P_local, Sval_local=None, flags=0):
         self.plan.execute(W_local, H, P_local, Sval_local, flags)
 
-    def execute_from_host(self, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0):
+    def execute_from_host(self, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0, h_slice_rows=None):
         """execute() with every operand in pinned host memory (see host_step)."""
         if not hasattr(self, "_staging"):
             self._staging = {}
-        host_step(self.plan, self.shard.rank, self.shard.world, W_host, H_host_slice, H_dev, P_host, Sval_host,
-                  flags, self._staging)
+        return host_step(self.plan, self.shard.rank, self.shard.world, W_host, H_host_slice, H_dev, P_host, Sval_host,
+                         flags, self._staging, h_slice_rows)
 
     def close(self):
         self.plan.close()

@@ -440,3 +440,28 @@ def test_pinned_host_operands_upload_only_touched_rows(monkeypatch):
     assert up_pinned < up_pageable <= 4 * K * (p["M"] + p["N"]) + 4 * nnz
     assert np.array_equal(Pp.numpy(), P_pageable)
     assert_parity(P_pageable, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+
+
+def test_used_lines_and_row_upload(engine):
+    import torch
+    rng = np.random.default_rng(7)
+    M, N, K = 300, 200, 36
+    rows = np.sort(rng.choice(np.arange(0, M, 3), 900)).astype(np.int32)       # two rows of three stay empty
+    cols = rng.choice(np.arange(1, N, 2), 900).astype(np.int32)                 # even columns stay empty
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    for which, ids_ref, n_lines in ((0, np.unique(rows), M), (1, np.unique(cols), N)):
+        ptr, n = plan.used_lines(which)
+        assert n == ids_ref.size
+        # the list lives in plan-owned device memory: it is checked through what the row upload moves
+        host = torch.from_numpy(rng.standard_normal((n_lines, K)).astype(np.float32)).pin_memory()
+        dev = torch.zeros((n_lines, K), device="cuda")
+        engine.upload_rows(host, dev, ptr, n, K, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        got = dev.cpu().numpy()
+        expect = np.zeros((n_lines, K), np.float32)
+        expect[ids_ref] = host.numpy()[ids_ref]
+        assert np.array_equal(got, expect)        # listed rows arrived, every other row untouched
+    # pageable host memory is refused before anything is launched
+    with pytest.raises(api.SddmmError):
+        engine.upload_rows(np.zeros((M, K), np.float32), torch.zeros((M, K), device="cuda"), plan.used_lines(0)[0], 1, K)
+    plan.close()
