@@ -139,8 +139,8 @@ SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
 /* Milliseconds of the kernels of the last synchronous sddmm_execute(), measured
  * with CUDA events on the compute stream -- the region the reference times and
  * prints as "Time for SDDMM with K = ..." (sddmm.cu:93,109-114).  For a pipelined
- * call (see sddmm_execute) it is the span from the first chunk's kernel to the
- * last one's, waits for the uploads in between included. */
+ * call (see sddmm_execute) it is the sum over the chunks' kernels; the waits for
+ * uploads between them are not counted. */
 SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
 
 /*

@@ -38,7 +38,8 @@ struct sddmm_handle_s {
     // pipelined execution with host operands: compute and download streams, one
     // "uploaded" and one "computed" event per chunk (created on first use)
     cudaStream_t pipe_compute = nullptr, pipe_download = nullptr;
-    cudaEvent_t pipe_uploaded[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_computed[SDDMM_PIPE_MAX_CHUNKS] = {};
+    cudaEvent_t pipe_uploaded[SDDMM_PIPE_MAX_CHUNKS] = {};
+    cudaEvent_t pipe_started[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_computed[SDDMM_PIPE_MAX_CHUNKS] = {};  // timing events
     cudaEvent_t pipe_joined = nullptr;
     bool pipeline = true;  // SDDMM_PIPELINE=0 keeps upload, kernel and download strictly one after the other
     // pipelined calls whose host operands are page-locked and mapped upload only the rows of
@@ -179,7 +180,8 @@ cudaError_t ensure_pipeline(sddmm_handle_s *h)
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->pipe_download, cudaStreamNonBlocking);
     for (int i = 0; i < SDDMM_PIPE_MAX_CHUNKS && e == cudaSuccess; ++i) {
         e = cudaEventCreateWithFlags(&h->pipe_uploaded[i], cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_computed[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreate(&h->pipe_started[i]);
+        if (e == cudaSuccess) e = cudaEventCreate(&h->pipe_computed[i]);
     }
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_joined, cudaEventDisableTiming);
     return e;
@@ -283,6 +285,7 @@ int sddmm_destroy(sddmm_handle_t h)
     if (h->pipe_compute) cudaStreamDestroy(h->pipe_compute);
     if (h->pipe_download) cudaStreamDestroy(h->pipe_download);
     for (cudaEvent_t e : h->pipe_uploaded) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->pipe_started) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : h->pipe_computed) if (e) cudaEventDestroy(e);
     if (h->pipe_joined) cudaEventDestroy(h->pipe_joined);
     (void)cudaGetLastError();
@@ -582,7 +585,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
                 CUDA_TRY(h, cudaMemcpyAsync(p->d_S + n0, Sval + n0, sizeof(float) * (size_t)cnt, cudaMemcpyHostToDevice, s));
             CUDA_TRY(h, cudaEventRecord(h->pipe_uploaded[i], s));
             CUDA_TRY(h, cudaStreamWaitEvent(h->pipe_compute, h->pipe_uploaded[i], 0));
-            if (i == 0) CUDA_TRY(h, cudaEventRecord(h->ev0, h->pipe_compute));
+            CUDA_TRY(h, cudaEventRecord(h->pipe_started[i], h->pipe_compute));
             CUDA_TRY(h, launch_ring(p->d_rows + n0, cols_p + n0, nullptr, dS ? dS + n0 : nullptr, dW, dH, dP + n0, cnt, p->K,
                                     p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status,
                                     h->pipe_compute));
@@ -593,14 +596,18 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
                                             h->pipe_download));
             }
         }
-        CUDA_TRY(h, cudaEventRecord(h->ev1, h->pipe_compute));
         // the caller's stream continues only after the last kernel and the last download
         cudaStream_t last = p_dev ? h->pipe_compute : h->pipe_download;
         CUDA_TRY(h, cudaEventRecord(h->pipe_joined, last));
         CUDA_TRY(h, cudaStreamWaitEvent(s, h->pipe_joined, 0));
         CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
         CUDA_TRY(h, cudaStreamSynchronize(s));
-        CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
+        p->last_ms = 0.f;  // kernel time only: the chunks' kernels, not the waits for uploads between them
+        for (int i = 0; i < p->n_pipe; ++i) {
+            float ms = 0.f;
+            CUDA_TRY(h, cudaEventElapsedTime(&ms, h->pipe_started[i], h->pipe_computed[i]));
+            p->last_ms += ms;
+        }
         return check_device_status(h);
     }
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
