@@ -305,6 +305,18 @@ SDDMM_API int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int
                              int64_t *nnz, char *errbuf, int errbuf_len);
 SDDMM_API int sddmm_mtx_read(sddmm_mtx_t f, int32_t *rows, int32_t *cols, float *vals);
 SDDMM_API int sddmm_mtx_close(sddmm_mtx_t f);
+/*
+ * Seeded synthetic matrix instead of a file (the reference ships no dataset: its
+ * dataset/ folder is empty and HiPC18/run.sh, scripts/ name public corpora that
+ * must be fetched).  `spec` is one of
+ *   uniform:M:N:density | zipf:M:N:nnz | rmat:scale:edge_factor | band:M:half_width:g
+ *   | c1 | c2 | c3 | c4 | c5        (the five benchmark configurations)
+ * optionally followed by ":seed=S".  The result is row-sorted (columns ascending
+ * inside a row, no duplicates) and is read with sddmm_mtx_read / released with
+ * sddmm_mtx_close like a parsed file.  Host code; deterministic for a given spec.
+ */
+SDDMM_API int sddmm_gen_open(const char *spec, sddmm_mtx_t *out, int64_t *M, int64_t *N,
+                             int64_t *nnz, char *errbuf, int errbuf_len);
 /* 0/1: whether the triples just read are sorted by row (what the engine needs). */
 SDDMM_API int sddmm_coo_is_row_sorted(int64_t nnz, const int32_t *rows);
 SDDMM_API int sddmm_mtx_write(const char *path, int64_t M, int64_t N, int64_t nnz,

@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
-    "sddmm_mtx_close", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
+    "sddmm_mtx_close", "sddmm_gen_open", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
 
 
@@ -89,6 +89,8 @@ def lib():
     L.sddmm_partition_rows.argtypes = [i64, i64, vp, C.c_int, C.c_int, vp, vp]
     L.sddmm_partition_rows_weighted.argtypes = [i64, i64, vp, C.c_int, C.c_int, C.c_double, vp, vp]
     L.sddmm_mtx_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
+                                 C.c_char_p, C.c_int]
+    L.sddmm_gen_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
                                  C.c_char_p, C.c_int]
     L.sddmm_mtx_read.argtypes = [vp, vp, vp, vp]
     L.sddmm_mtx_close.argtypes = [vp]
@@ -301,6 +303,23 @@ def mtx_read(path):
     M, N, nnz = C.c_int64(), C.c_int64(), C.c_int64()
     err = C.create_string_buffer(256)
     st = lib().sddmm_mtx_open(os.fsencode(path), C.byref(f), C.byref(M), C.byref(N), C.byref(nnz), err, 256)
+    if st != OK:
+        raise SddmmError(st, err.value.decode())
+    rows = np.empty(nnz.value, np.int32)
+    cols = np.empty(nnz.value, np.int32)
+    vals = np.empty(nnz.value, np.float32)
+    st = lib().sddmm_mtx_read(f, rows.ctypes.data, cols.ctypes.data, vals.ctypes.data)
+    if st != OK:
+        raise SddmmError(st)
+    return M.value, N.value, rows, cols, vals
+
+
+def gen_matrix(spec):
+    """Seeded synthetic matrix (see sddmm_gen_open): (M, N, rows, cols, vals), row-sorted."""
+    f = C.c_void_p()
+    M, N, nnz = C.c_int64(), C.c_int64(), C.c_int64()
+    err = C.create_string_buffer(256)
+    st = lib().sddmm_gen_open(spec.encode(), C.byref(f), C.byref(M), C.byref(N), C.byref(nnz), err, 256)
     if st != OK:
         raise SddmmError(st, err.value.decode())
     rows = np.empty(nnz.value, np.int32)

@@ -12,13 +12,9 @@
 #include <string>
 #include <vector>
 
+#include "mtx_holder.hpp"
 #include "sddmm_b200.h"
 
-struct sddmm_mtx_s {
-    int64_t M = 0, N = 0, nnz = 0;
-    std::vector<int32_t> rows, cols;
-    std::vector<float> vals;
-};
 
 namespace {
 

@@ -1,6 +1,12 @@
 // Drop-in command line of the reference program:
 //
 //     ./sddmm input.mtx K tile_size_X tile_size_Y [options]
+//     ./sddmm gen:SPEC  K tile_size_X tile_size_Y [options]
+//
+// The second form takes a seeded synthetic matrix instead of a file (the
+// reference ships no dataset): gen:c1 .. gen:c5 are the benchmark configurations,
+// gen:uniform:M:N:density, gen:zipf:M:N:nnz, gen:rmat:scale:edge_factor and
+// gen:band:M:half_width:g the generators behind them (see sddmm_gen_open).
 //
 // Same four positionals in the same order and with the meaning the reference's
 // code gives them (HiPC18/src/sddmm.cu:251-255): argv[3] is the row-panel height
@@ -21,6 +27,8 @@
 //   --device D         CUDA device (default 0)
 //   --dump-p FILE      write P (float32, input nonzero order) to FILE
 //   --json FILE        write a small JSON report (ms, GFLOP/s, plan sizes)
+//   --write-mtx FILE   write the input matrix as Matrix Market (e.g. to hand a
+//                      generated matrix to another program)
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -50,7 +58,9 @@ int main(int argc, char **argv)
 {
     if (argc < 5) {
         std::fprintf(stderr, "usage: %s input.mtx K tile_size_X tile_size_Y [--iters N] [--warmup N] "
-                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE]\n", argv[0]);
+                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE]\n"
+                             "       input may be gen:c1..c5 | gen:uniform:M:N:density | gen:zipf:M:N:nnz | "
+                             "gen:rmat:scale:edge_factor | gen:band:M:half_width:g [:seed=S]\n", argv[0]);
         return 2;
     }
     const char *path = argv[1];
@@ -59,7 +69,7 @@ int main(int argc, char **argv)
     const int col_tile = std::atoi(argv[4]);    // tile_sizeX in the reference
     int iters = 1, warmup = 0, device = 0;
     bool scale = true, gather = false;
-    const char *dump_p = nullptr, *json = nullptr;
+    const char *dump_p = nullptr, *json = nullptr, *write_mtx = nullptr;
     for (int i = 5; i < argc; ++i) {
         std::string a = argv[i];
         auto need = [&](const char *name) -> const char * {
@@ -77,6 +87,7 @@ int main(int argc, char **argv)
         else if (a == "--gather") gather = true;
         else if (a == "--dump-p") dump_p = need("--dump-p");
         else if (a == "--json") json = need("--json");
+        else if (a == "--write-mtx") write_mtx = need("--write-mtx");
         else {
             std::fprintf(stderr, "sddmm: unknown option %s\n", a.c_str());
             return 2;
@@ -87,14 +98,20 @@ int main(int argc, char **argv)
     sddmm_mtx_t f = nullptr;
     int64_t M = 0, N = 0, nnz = 0;
     char err[256] = "";
-    int st = sddmm_mtx_open(path, &f, &M, &N, &nnz, err, sizeof(err));
-    if (st != SDDMM_OK) return die("reading input", st, err);
+    const bool generated = std::strncmp(path, "gen:", 4) == 0;
+    int st = generated ? sddmm_gen_open(path + 4, &f, &M, &N, &nnz, err, sizeof(err))
+                       : sddmm_mtx_open(path, &f, &M, &N, &nnz, err, sizeof(err));
+    if (st != SDDMM_OK) return die(generated ? "generating input" : "reading input", st, err);
     std::printf("\nMatrix info:  rows: %lld, cols: %lld, nnz: %lld\n", (long long)M, (long long)N, (long long)nnz);
     std::vector<int32_t> rows((size_t)nnz), cols((size_t)nnz);
     std::vector<float> vals((size_t)nnz);
     st = sddmm_mtx_read(f, rows.data(), cols.data(), vals.data());
     if (st != SDDMM_OK) return die("reading input", st, "");
     std::printf("\nTilesize: X = %d, tilesize: Y = %d, TB: %d\n", col_tile, panel_rows, 256);
+    if (write_mtx) {
+        st = sddmm_mtx_write(write_mtx, M, N, nnz, rows.data(), cols.data(), vals.data());
+        if (st != SDDMM_OK) return die("writing the matrix", st, write_mtx);
+    }
     if (!sddmm_coo_is_row_sorted(nnz, rows.data()))
         return die("input", SDDMM_UNSORTED_INPUT, "convert it with sddmm_coo_sort_rows first");
 

@@ -312,7 +312,19 @@ def test_cli_prints_reference_lines_and_matches_oracle(tmp_path):
         W = oracle.cpu.initial(M, K)     # the reference's operand initialisation
         H = oracle.cpu.initial(N, K)
         assert_parity(np.fromfile(out, np.float32), rows, cols, W, H, sv)
+    # a generated input instead of a file: the matrix written by --write-mtx is the one that was computed on
+    gen_mtx = str(tmp_path / "gen.mtx")
+    res = subprocess.run([exe, "gen:rmat:11:12:seed=5", "64", "96", "50000", "--dump-p", out, "--write-mtx", gen_mtx],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    gM, gN, g_rows, g_cols, g_vals = api.mtx_read(gen_mtx)
+    m2 = api.gen_matrix("rmat:11:12:seed=5")
+    assert (gM, gN) == (2048, 2048) and np.array_equal(g_rows, m2[2]) and np.array_equal(g_cols, m2[3])
+    assert res.stdout.splitlines()[1] == f"Matrix info:  rows: 2048, cols: 2048, nnz: {g_rows.size}"
+    assert_parity(np.fromfile(out, np.float32), g_rows, g_cols, oracle.cpu.initial(gM, 64), oracle.cpu.initial(gN, 64), g_vals)
     # errors: non-zero exit code and one line on stderr instead of an assert
+    bad = subprocess.run([exe, "gen:nosuch", "32", "192", "50000"], capture_output=True, text=True)
+    assert bad.returncode != 0 and bad.stderr.startswith("sddmm: ")
     bad = subprocess.run([exe, str(tmp_path / "missing.mtx"), "32", "192", "50000"], capture_output=True, text=True)
     assert bad.returncode != 0 and bad.stderr.startswith("sddmm: ")
     bad = subprocess.run([exe, mtx, "30", "192", "50000"], capture_output=True, text=True)

@@ -172,3 +172,63 @@ def test_weighted_partition_moves_cuts_towards_short_rows():
     for parts in (3, 8):
         c, z = api.partition_rows(M, rows, parts, 32, row_cost=2.0)
         assert c[0] == 0 and c[-1] == M and np.all(np.diff(c) >= 0) and z[-1] == rows.size
+
+
+# ---- seeded synthetic matrices (sddmm_gen_open) ---------------------------------
+
+def _is_row_sorted_unique(M, N, rows, cols):
+    key = rows.astype(np.int64) * N + cols
+    return bool(np.all(np.diff(key) > 0)) and rows.min() >= 0 and rows.max() < M and cols.min() >= 0 and cols.max() < N
+
+
+def test_generators_have_the_benchmark_shapes():
+    M, N, rows, cols, vals = api.gen_matrix("c1")
+    assert (M, N, rows.size) == (4096, 4096, 16777) and _is_row_sorted_unique(M, N, rows, cols)
+    assert np.all(vals == 1.0)
+    M, N, rows, cols, vals = api.gen_matrix("c2")
+    assert (M, N, rows.size) == (12419, 1500, 746316) and _is_row_sorted_unique(M, N, rows, cols)
+    assert np.all(vals == np.round(vals)) and vals.min() >= 1 and vals.max() <= 20
+    lengths = np.bincount(rows, minlength=M)
+    assert lengths.max() <= N and lengths.max() > 20 * max(np.median(lengths), 1)     # heavy-tailed rows
+    col_pop = np.bincount(cols, minlength=N)
+    assert col_pop[:50].mean() > 5 * col_pop[-500:].mean()                          # popular columns first
+
+
+def test_rmat_generator_is_skewed_and_deduplicated():
+    scale, ef = 12, 8
+    M, N, rows, cols, vals = api.gen_matrix(f"rmat:{scale}:{ef}")
+    assert M == N == 1 << scale and _is_row_sorted_unique(M, N, rows, cols)
+    assert 0.7 * ef * M < rows.size <= ef * M                                      # duplicates removed
+    half = M // 2
+    quad_a = np.mean((rows < half) & (cols < half))
+    quad_d = np.mean((rows >= half) & (cols >= half))
+    assert 0.45 < quad_a < 0.60 and 0.03 < quad_d < 0.09                           # (a, d) = (0.57, 0.05) before dedup
+    assert abs(float(vals.mean())) < 0.02 and 0.97 < float(vals.std()) < 1.03      # normal(0, 1)
+
+
+def test_band_generator_counts():
+    M, hw, g = 700, 9, 4
+    _, _, rows, cols, vals = api.gen_matrix(f"band:{M}:{hw}:{g}")
+    assert _is_row_sorted_unique(M, M, rows, cols)
+    lengths = np.bincount(rows, minlength=M)
+    full_rows = np.nonzero(lengths == M)[0]
+    col_len = np.bincount(cols, minlength=M)
+    full_cols = np.nonzero(col_len == M)[0]
+    assert full_rows.size == g and full_cols.size == g
+    inside = np.abs(rows.astype(np.int64) - cols) <= hw
+    expect_band = sum(min(M - 1, i + hw) - max(0, i - hw) + 1 for i in range(M))
+    assert inside.sum() == expect_band
+    outside = ~inside
+    assert np.all(np.isin(rows[outside], full_rows) | np.isin(cols[outside], full_cols))
+
+
+def test_generators_are_deterministic_and_seeded():
+    a = api.gen_matrix("uniform:300:200:0.05")
+    b = api.gen_matrix("uniform:300:200:0.05")
+    c = api.gen_matrix("uniform:300:200:0.05:seed=9")
+    assert a[2].size == b[2].size == c[2].size == 3000
+    assert np.array_equal(a[2], b[2]) and np.array_equal(a[3], b[3])
+    assert not (np.array_equal(a[2], c[2]) and np.array_equal(a[3], c[3]))
+    for bad in ("nosuch:1:2", "uniform:10:10:1.5", "rmat:40:2", "band:10:1:11", "uniform:10:10:0.1:seed=x"):
+        with pytest.raises(api.SddmmError):
+            api.gen_matrix(bad)
