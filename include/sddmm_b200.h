@@ -296,14 +296,41 @@ SDDMM_API int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_
  * and comment lines, reads "M N nnz", then nnz triples "row col val" (1-based).
  * Accepts everything the reference accepts; additionally accepts a size line that
  * is the first line and `pattern` files (value 1.0), expands `symmetric` only on
- * request, and reports what the reference silently mis-parses as
+ * request (sddmm_mtx_open_ex), and reports what the reference silently mis-parses as
  * SDDMM_PARSE_ERROR.  Two-call protocol: sddmm_mtx_open reads the file and
  * reports the sizes, sddmm_mtx_read copies into caller buffers and closes.
  */
 typedef struct sddmm_mtx_s *sddmm_mtx_t;
 SDDMM_API int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N,
                              int64_t *nnz, char *errbuf, int errbuf_len);
+/*
+ * The same reader with options, and with the formats found around the reference's
+ * loaders: Matrix Market `general` / `symmetric` / `skew-symmetric`, fields
+ * `real` / `integer` / `pattern`; the three sizes on one line or on three
+ * (headerless bag-of-words "docword" files, which the reference's other readers
+ * take with `fp >> n_rows >> n_cols >> nnz`,
+ * other_ideas/our_work/sparse_dense_split/sddmm.cu:356); and the binary form
+ * written by sddmm_coo_save_binary (recognised by its first bytes).
+ *   SDDMM_MTX_EXPAND_SYMMETRIC : a symmetric file stores one triangle -- add the
+ *       mirror image of every off-diagonal entry (negated for skew-symmetric).
+ *       Without the flag the stored triangle is returned as is, which is what
+ *       the reference does (it ignores the banner, sddmm.cu:257-261).
+ *   SDDMM_MTX_SORT_ROWS : return the triples sorted by (row, col) (stable), as
+ *       sddmm_plan_coo needs them; sorted input is left untouched.
+ */
+#define SDDMM_MTX_EXPAND_SYMMETRIC 0x1u
+#define SDDMM_MTX_SORT_ROWS 0x2u
+SDDMM_API int sddmm_mtx_open_ex(const char *path, uint32_t flags, sddmm_mtx_t *out, int64_t *M,
+                                int64_t *N, int64_t *nnz, char *errbuf, int errbuf_len);
 SDDMM_API int sddmm_mtx_read(sddmm_mtx_t f, int32_t *rows, int32_t *cols, float *vals);
+/*
+ * Binary form of a COO matrix (48-byte header with a checksum, then rows, cols
+ * and, unless vals is NULL, values; little-endian, 0-based): the reference
+ * re-parses the text file on every run (sddmm.cu:274-281), this loads at the
+ * speed of the disk.  Read it back with sddmm_mtx_open / sddmm_mtx_open_ex.
+ */
+SDDMM_API int sddmm_coo_save_binary(const char *path, int64_t M, int64_t N, int64_t nnz,
+                                    const int32_t *rows, const int32_t *cols, const float *vals);
 SDDMM_API int sddmm_mtx_close(sddmm_mtx_t f);
 /*
  * Seeded synthetic matrix instead of a file (the reference ships no dataset: its
@@ -332,6 +359,16 @@ SDDMM_API int sddmm_mtx_write(const char *path, int64_t M, int64_t N, int64_t nn
  */
 SDDMM_API int sddmm_coo_sort_rows(int64_t *M, int64_t *N, int64_t nnz, int32_t *rows,
                                   int32_t *cols, float *vals, int transpose);
+
+/*
+ * The same conversion on the GPU (radix sorts instead of std::sort; seconds become
+ * milliseconds at 10^8 nonzeros).  Results are identical to sddmm_coo_sort_rows:
+ * transpose = 0 keeps the input order of equal (row, col) pairs, transpose = 1
+ * orders whole (col, row, val) tuples.  rows / cols / vals may be host or device
+ * arrays (rows and cols both of the same kind); sorted in place.
+ */
+SDDMM_API int sddmm_coo_sort_rows_gpu(sddmm_handle_t h, int64_t *M, int64_t *N, int64_t nnz,
+                                      int32_t *rows, int32_t *cols, float *vals, int transpose);
 
 #ifdef __cplusplus
 }

@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
-    "sddmm_mtx_close", "sddmm_gen_open", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
+    "sddmm_mtx_close", "sddmm_mtx_open_ex", "sddmm_coo_save_binary", "sddmm_coo_sort_rows_gpu", "sddmm_gen_open", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
 
 
@@ -90,6 +90,10 @@ def lib():
     L.sddmm_partition_rows_weighted.argtypes = [i64, i64, vp, C.c_int, C.c_int, C.c_double, vp, vp]
     L.sddmm_mtx_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
                                  C.c_char_p, C.c_int]
+    L.sddmm_mtx_open_ex.argtypes = [C.c_char_p, u32, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
+                                    C.c_char_p, C.c_int]
+    L.sddmm_coo_save_binary.argtypes = [C.c_char_p, i64, i64, i64, vp, vp, vp]
+    L.sddmm_coo_sort_rows_gpu.argtypes = [vp, C.POINTER(i64), C.POINTER(i64), i64, vp, vp, vp, C.c_int]
     L.sddmm_gen_open.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
                                  C.c_char_p, C.c_int]
     L.sddmm_mtx_read.argtypes = [vp, vp, vp, vp]
@@ -164,6 +168,13 @@ class Handle:
         reads the host rows); `d_row_ids` is a device int32 tensor or a device address."""
         self._check(lib().sddmm_upload_rows(self._h, _ptr(host), _ptr(dev), _ptr(d_row_ids), n_rows, K,
                                             cuda_stream))
+
+    def coo_sort_rows(self, M, N, rows, cols, vals, transpose=False):
+        """sddmm_coo_sort_rows on the GPU, in place (numpy arrays or device tensors); returns (M, N)."""
+        m, n = C.c_int64(M), C.c_int64(N)
+        self._check(lib().sddmm_coo_sort_rows_gpu(self._h, C.byref(m), C.byref(n), rows.shape[0], _ptr(rows), _ptr(cols),
+                                                  _ptr(vals), 1 if transpose else 0))
+        return m.value, n.value
 
     def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, col_tile_hint=0, flags=0, nnz=None):
         if nnz is None:
@@ -297,12 +308,17 @@ def partition_rows(M, rows, n_parts, align_rows=1, row_cost=0.0):
     return cuts, nnz_cuts
 
 
-def mtx_read(path):
-    """Returns (M, N, rows, cols, vals) with 0-based int32 indices."""
+MTX_EXPAND_SYMMETRIC = 0x1
+MTX_SORT_ROWS = 0x2
+
+
+def mtx_read(path, flags=0):
+    """Returns (M, N, rows, cols, vals) with 0-based int32 indices.  Reads Matrix Market text,
+    headerless docword triples and the binary form of coo_save_binary; flags: MTX_*."""
     f = C.c_void_p()
     M, N, nnz = C.c_int64(), C.c_int64(), C.c_int64()
     err = C.create_string_buffer(256)
-    st = lib().sddmm_mtx_open(os.fsencode(path), C.byref(f), C.byref(M), C.byref(N), C.byref(nnz), err, 256)
+    st = lib().sddmm_mtx_open_ex(os.fsencode(path), flags, C.byref(f), C.byref(M), C.byref(N), C.byref(nnz), err, 256)
     if st != OK:
         raise SddmmError(st, err.value.decode())
     rows = np.empty(nnz.value, np.int32)
@@ -312,6 +328,12 @@ def mtx_read(path):
     if st != OK:
         raise SddmmError(st)
     return M.value, N.value, rows, cols, vals
+
+
+def coo_save_binary(path, M, N, rows, cols, vals=None):
+    st = lib().sddmm_coo_save_binary(os.fsencode(path), M, N, rows.shape[0], _ptr(rows), _ptr(cols), _ptr(vals))
+    if st != OK:
+        raise SddmmError(st)
 
 
 def gen_matrix(spec):

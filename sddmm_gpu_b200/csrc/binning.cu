@@ -288,6 +288,84 @@ cudaError_t select_flagged_ids(const unsigned char *flag, int64_t n, int32_t **d
 
 }  // namespace
 
+namespace {
+
+__global__ void iota_kernel(int32_t *idx, int64_t n)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        idx[i] = (int32_t)i;
+}
+// floats -> unsigned keys with the same order
+__global__ void value_keys_kernel(const float *__restrict__ v, int64_t n, uint32_t *keys)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t u = __float_as_uint(v[i]);
+        keys[i] = u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
+    }
+}
+__global__ void pair_keys_kernel(const int32_t *__restrict__ a, const int32_t *__restrict__ b,
+                                 const int32_t *__restrict__ idx, int64_t n, unsigned long long *keys)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t j = idx[i];
+        keys[i] = ((unsigned long long)(uint32_t)a[j] << 32) | (uint32_t)b[j];
+    }
+}
+__global__ void gather_triples_kernel(const int32_t *__restrict__ idx, const int32_t *__restrict__ a,
+                                      const int32_t *__restrict__ b, const float *__restrict__ v, int64_t n,
+                                      int32_t *a_out, int32_t *b_out, float *v_out)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t j = idx[i];
+        a_out[i] = a[j];
+        b_out[i] = b[j];
+        v_out[i] = v[j];
+    }
+}
+
+}  // namespace
+
+cudaError_t sort_coo(int32_t *d_a, int32_t *d_b, float *d_v, int64_t nnz, bool tie_by_value, cudaStream_t stream)
+{
+    if (nnz <= 1) return cudaSuccess;
+    const size_t n = (size_t)nnz;
+    Scratch buf;  // keys64 in | keys64 out | idx A | idx B | sorted a, b, v
+    CK(buf.reserve(n * (8 + 8 + 4 + 4 + 4 + 4 + 4) + 64));
+    unsigned long long *k_in = (unsigned long long *)buf.ptr, *k_out = k_in + n;
+    int32_t *idx_a = (int32_t *)(k_out + n), *idx_b = idx_a + n;
+    int32_t *a_s = idx_b + n, *b_s = a_s + n;
+    float *v_s = (float *)(b_s + n);
+    iota_kernel<<<grid_for(nnz), TPB, 0, stream>>>(idx_a, nnz);
+    CK(cudaGetLastError());
+    Scratch tmp;
+    if (tie_by_value) {
+        // first by value; the stable sort by (a, b) that follows keeps that order inside equal pairs
+        uint32_t *vk_in = (uint32_t *)k_in, *vk_out = vk_in + n;
+        value_keys_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_v, nnz, vk_in);
+        CK(cudaGetLastError());
+        size_t tb = 0;
+        CK(cub::DeviceRadixSort::SortPairs(nullptr, tb, vk_in, vk_out, idx_a, idx_b, (int)nnz, 0, 32, stream));
+        CK(tmp.reserve(tb));
+        CK(cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, vk_in, vk_out, idx_a, idx_b, (int)nnz, 0, 32, stream));
+        std::swap(idx_a, idx_b);
+    }
+    pair_keys_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_a, d_b, idx_a, nnz, k_in);
+    CK(cudaGetLastError());
+    size_t tb = 0;
+    CK(cub::DeviceRadixSort::SortPairs(nullptr, tb, k_in, k_out, idx_a, idx_b, (int)nnz, 0, 64, stream));
+    if (tb > tmp.bytes) {
+        tmp.release();
+        CK(tmp.reserve(tb));
+    }
+    CK(cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, k_in, k_out, idx_a, idx_b, (int)nnz, 0, 64, stream));
+    gather_triples_kernel<<<grid_for(nnz), TPB, 0, stream>>>(idx_b, d_a, d_b, d_v, nnz, a_s, b_s, v_s);
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(d_a, a_s, sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, stream));
+    CK(cudaMemcpyAsync(d_b, b_s, sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, stream));
+    CK(cudaMemcpyAsync(d_v, v_s, sizeof(float) * n, cudaMemcpyDeviceToDevice, stream));
+    return cudaStreamSynchronize(stream);
+}
+
 cudaError_t build_used_row_list(const int64_t *d_row_ptr, int64_t M, int32_t **d_list, int64_t *n_list,
                                 cudaStream_t stream)
 {

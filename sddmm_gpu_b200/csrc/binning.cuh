@@ -60,6 +60,12 @@ cudaError_t build_used_row_list(const int64_t *d_row_ptr, int64_t M, int32_t **d
 cudaError_t build_used_col_list(const int32_t *d_cols, int64_t nnz, int64_t N, int32_t **d_list, int64_t *n_list,
                                 cudaStream_t stream);
 
+// Sort COO triples on the device, in place: by (a, b) keeping the input order of
+// equal pairs (stable), or -- tie_by_value -- by (a, b, value), the order
+// std::sort gives whole (a, b, value) tuples.  d_a / d_b are the major / minor
+// index arrays (rows / cols, or cols / rows for a transposing sort).
+cudaError_t sort_coo(int32_t *d_a, int32_t *d_b, float *d_v, int64_t nnz, bool tie_by_value, cudaStream_t stream);
+
 // Hub-column hints for the ring kernel: d_cols_hinted[j] = d_cols_p[j] with bit 31
 // set when the column is among the most popular ones whose rows of H together fit
 // budget_bytes (chosen by exact column degree, most popular first).

@@ -658,6 +658,60 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     return check_device_status(h);
 }
 
+int sddmm_coo_sort_rows_gpu(sddmm_handle_t h, int64_t *M, int64_t *N, int64_t nnz, int32_t *rows, int32_t *cols,
+                            float *vals, int transpose)
+{
+    if (!h || !M || !N || nnz < 0 || nnz >= INT32_MAX || (nnz > 0 && (!rows || !cols || !vals))) return SDDMM_INVALID_ARG;
+    if (nnz > 0) {
+        CUDA_TRY(h, cudaSetDevice(h->device));
+        cudaStream_t s = h->stream;
+        const bool idx_dev = is_device_ptr(rows), val_dev = is_device_ptr(vals);
+        if (idx_dev != is_device_ptr(cols)) {
+            h->last_error = "sddmm_coo_sort_rows_gpu: rows and cols must both be host or both be device arrays";
+            return SDDMM_INVALID_ARG;
+        }
+        struct Tmp {
+            void *p[3] = {nullptr, nullptr, nullptr};
+            ~Tmp() { for (void *q : p) if (q) cudaFree(q); }
+        } tmp;
+        const size_t bytes = 4 * (size_t)nnz;
+        int32_t *d_rows = rows, *d_cols = cols;
+        float *d_vals = vals;
+        if (!idx_dev) {
+            CUDA_TRY(h, cudaMalloc(&tmp.p[0], bytes));
+            CUDA_TRY(h, cudaMalloc(&tmp.p[1], bytes));
+            d_rows = (int32_t *)tmp.p[0];
+            d_cols = (int32_t *)tmp.p[1];
+            CUDA_TRY(h, cudaMemcpyAsync(d_rows, rows, bytes, cudaMemcpyHostToDevice, s));
+            CUDA_TRY(h, cudaMemcpyAsync(d_cols, cols, bytes, cudaMemcpyHostToDevice, s));
+        }
+        if (!val_dev) {
+            CUDA_TRY(h, cudaMalloc(&tmp.p[2], bytes));
+            d_vals = (float *)tmp.p[2];
+            CUDA_TRY(h, cudaMemcpyAsync(d_vals, vals, bytes, cudaMemcpyHostToDevice, s));
+        }
+        // transposing: the reference sorts whole (col, row, val) tuples and then swaps the roles
+        // (util.h:88-104): the old columns become the rows of the result
+        if (transpose) CUDA_TRY(h, sort_coo(d_cols, d_rows, d_vals, nnz, true, s));
+        else CUDA_TRY(h, sort_coo(d_rows, d_cols, d_vals, nnz, false, s));
+        const int32_t *new_rows = transpose ? d_cols : d_rows, *new_cols = transpose ? d_rows : d_cols;
+        if (!idx_dev) {
+            CUDA_TRY(h, cudaMemcpyAsync(rows, new_rows, bytes, cudaMemcpyDeviceToHost, s));
+            CUDA_TRY(h, cudaMemcpyAsync(cols, new_cols, bytes, cudaMemcpyDeviceToHost, s));
+        } else if (transpose) {
+            // device arrays: exchange the contents of rows and cols through a scratch copy
+            CUDA_TRY(h, cudaMalloc(&tmp.p[0], bytes));
+            CUDA_TRY(h, cudaMemcpyAsync(tmp.p[0], rows, bytes, cudaMemcpyDeviceToDevice, s));
+            CUDA_TRY(h, cudaMemcpyAsync(rows, cols, bytes, cudaMemcpyDeviceToDevice, s));
+            CUDA_TRY(h, cudaMemcpyAsync(cols, tmp.p[0], bytes, cudaMemcpyDeviceToDevice, s));
+        }
+        if (!val_dev) CUDA_TRY(h, cudaMemcpyAsync(vals, d_vals, bytes, cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(h, cudaStreamSynchronize(s));
+    }
+    if (transpose) std::swap(*M, *N);
+    return SDDMM_OK;
+}
+
 int sddmm_plan_used_lines(sddmm_plan_t p, int which, const int32_t **d_ids, int64_t *n)
 {
     if (!p || !d_ids || !n || (which != 0 && which != 1)) return SDDMM_INVALID_ARG;

@@ -65,6 +65,132 @@ inline const char *parse_f32(const char *p, const char *end, float *out)
     return p + n;
 }
 
+// ---- binary form of a COO matrix: header, rows, cols, [vals]; little-endian ----
+const char BIN_MAGIC[8] = {'S', 'D', 'D', 'M', 'M', 'C', 'O', 'O'};
+struct BinHeader {
+    char magic[8];
+    uint32_t version, flags;  // flags bit 0: values present
+    int64_t M, N, nnz;
+    uint64_t checksum;        // over rows, cols, vals as stored
+};
+static_assert(sizeof(BinHeader) == 48, "binary header layout");
+
+// 64-bit multiply-xorshift over 8-byte words (tail bytes zero-extended), chained through `h`.
+uint64_t checksum(uint64_t h, const void *data, size_t bytes)
+{
+    const unsigned char *p = (const unsigned char *)data;
+    size_t i = 0;
+    for (; i + 8 <= bytes; i += 8) {
+        uint64_t w;
+        std::memcpy(&w, p + i, 8);
+        h = (h ^ w) * 0x9E3779B97F4A7C15ull;
+        h ^= h >> 29;
+    }
+    if (i < bytes) {
+        uint64_t w = 0;
+        std::memcpy(&w, p + i, bytes - i);
+        h = (h ^ w) * 0x9E3779B97F4A7C15ull;
+        h ^= h >> 29;
+    }
+    return h;
+}
+
+// `f` is positioned after the magic.
+int load_binary(FILE *f, sddmm_mtx_s **out, char *errbuf, int errbuf_len)
+{
+    BinHeader h;
+    if (std::fread((char *)&h + 8, sizeof(h) - 8, 1, f) != 1) {
+        set_err(errbuf, errbuf_len, "binary matrix: truncated header");
+        return SDDMM_PARSE_ERROR;
+    }
+    if (h.version != 1 || h.M < 0 || h.N < 0 || h.nnz < 0 || h.M > INT32_MAX || h.N > INT32_MAX || h.nnz >= INT32_MAX) {
+        set_err(errbuf, errbuf_len, "binary matrix: unsupported version or sizes out of range");
+        return SDDMM_PARSE_ERROR;
+    }
+    sddmm_mtx_s *mx = new (std::nothrow) sddmm_mtx_s;
+    if (!mx) return SDDMM_OUT_OF_MEMORY;
+    mx->M = h.M; mx->N = h.N; mx->nnz = h.nnz;
+    const size_t z = (size_t)h.nnz;
+    try {
+        mx->rows.resize(z);
+        mx->cols.resize(z);
+        mx->vals.assign(z, 1.0f);
+    } catch (...) {
+        delete mx;
+        return SDDMM_OUT_OF_MEMORY;
+    }
+    bool ok = z == 0 || std::fread(mx->rows.data(), sizeof(int32_t), z, f) == z;
+    ok = ok && (z == 0 || std::fread(mx->cols.data(), sizeof(int32_t), z, f) == z);
+    if (h.flags & 1u) ok = ok && (z == 0 || std::fread(mx->vals.data(), sizeof(float), z, f) == z);
+    if (!ok) {
+        set_err(errbuf, errbuf_len, "binary matrix: truncated payload");
+        delete mx;
+        return SDDMM_PARSE_ERROR;
+    }
+    uint64_t sum = 0;
+    sum = checksum(sum, mx->rows.data(), sizeof(int32_t) * z);
+    sum = checksum(sum, mx->cols.data(), sizeof(int32_t) * z);
+    if (h.flags & 1u) sum = checksum(sum, mx->vals.data(), sizeof(float) * z);
+    if (sum != h.checksum) {
+        set_err(errbuf, errbuf_len, "binary matrix: checksum mismatch");
+        delete mx;
+        return SDDMM_PARSE_ERROR;
+    }
+    for (size_t i = 0; i < z; ++i)
+        if (mx->rows[i] < 0 || mx->rows[i] >= h.M || mx->cols[i] < 0 || mx->cols[i] >= h.N) {
+            set_err(errbuf, errbuf_len, "binary matrix: index out of range");
+            delete mx;
+            return SDDMM_INDEX_OUT_OF_RANGE;
+        }
+    *out = mx;
+    return SDDMM_OK;
+}
+
+// What the open flags ask for after the triples are in memory.
+int finish_open(sddmm_mtx_s *mx, uint32_t flags, int symmetric, char *errbuf, int errbuf_len)
+{
+    try {
+        if ((flags & SDDMM_MTX_EXPAND_SYMMETRIC) && symmetric != 0) {
+            // a symmetric file stores one triangle: add the mirror image of every off-diagonal entry
+            if (mx->M != mx->N) {
+                set_err(errbuf, errbuf_len, "a symmetric matrix must be square");
+                return SDDMM_PARSE_ERROR;
+            }
+            const size_t z = (size_t)mx->nnz;
+            size_t extra = 0;
+            for (size_t i = 0; i < z; ++i) extra += mx->rows[i] != mx->cols[i];
+            if (z + extra >= (size_t)INT32_MAX) {
+                set_err(errbuf, errbuf_len, "matrix too large for 32-bit indices once expanded");
+                return SDDMM_PARSE_ERROR;
+            }
+            mx->rows.reserve(z + extra);
+            mx->cols.reserve(z + extra);
+            mx->vals.reserve(z + extra);
+            for (size_t i = 0; i < z; ++i)
+                if (mx->rows[i] != mx->cols[i]) {
+                    mx->rows.push_back(mx->cols[i]);
+                    mx->cols.push_back(mx->rows[i]);
+                    mx->vals.push_back(symmetric < 0 ? -mx->vals[i] : mx->vals[i]);
+                }
+            mx->nnz = (int64_t)(z + extra);
+        }
+        if (flags & SDDMM_MTX_SORT_ROWS) {
+            bool sorted = true;
+            for (int64_t i = 1; i < mx->nnz && sorted; ++i)
+                sorted = mx->rows[(size_t)i - 1] < mx->rows[(size_t)i] ||
+                         (mx->rows[(size_t)i - 1] == mx->rows[(size_t)i] && mx->cols[(size_t)i - 1] <= mx->cols[(size_t)i]);
+            if (!sorted) {
+                const int st = sddmm_coo_sort_rows(&mx->M, &mx->N, mx->nnz, mx->rows.data(), mx->cols.data(),
+                                                   mx->vals.data(), 0);
+                if (st != SDDMM_OK) return st;
+            }
+        }
+    } catch (const std::bad_alloc &) {
+        return SDDMM_OUT_OF_MEMORY;
+    }
+    return SDDMM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -72,12 +198,37 @@ extern "C" {
 int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N, int64_t *nnz, char *errbuf,
                    int errbuf_len)
 {
+    return sddmm_mtx_open_ex(path, 0u, out, M, N, nnz, errbuf, errbuf_len);
+}
+
+int sddmm_mtx_open_ex(const char *path, uint32_t flags, sddmm_mtx_t *out, int64_t *M, int64_t *N, int64_t *nnz,
+                      char *errbuf, int errbuf_len)
+{
     if (!path || !out) return SDDMM_INVALID_ARG;
     *out = nullptr;
     FILE *f = std::fopen(path, "rb");
     if (!f) {
         set_err(errbuf, errbuf_len, std::string("cannot open ") + path + ": " + std::strerror(errno));
         return SDDMM_IO_ERROR;
+    }
+    {
+        // the binary form written by sddmm_coo_save_binary is recognised by its first eight bytes
+        char magic[8] = {0};
+        const size_t got = std::fread(magic, 1, 8, f);
+        if (got == 8 && std::memcmp(magic, BIN_MAGIC, 8) == 0) {
+            sddmm_mtx_s *mx = nullptr;
+            int st = load_binary(f, &mx, errbuf, errbuf_len);
+            std::fclose(f);
+            if (st != SDDMM_OK) return st;
+            st = finish_open(mx, flags, /*symmetric*/0, errbuf, errbuf_len);
+            if (st != SDDMM_OK) { delete mx; return st; }
+            if (M) *M = mx->M;
+            if (N) *N = mx->N;
+            if (nnz) *nnz = mx->nnz;
+            *out = mx;
+            return SDDMM_OK;
+        }
+        std::fseek(f, 0, SEEK_SET);
     }
     std::vector<char> text;
     {
@@ -99,6 +250,7 @@ int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N, i
     // character is a digit (sddmm.cu:257-261); here a line is skipped when it is
     // empty or starts with '%', and the banner's field / symmetry words are read.
     bool pattern = false;
+    int symmetric = 0;  // 0 general, +1 symmetric (or hermitian), -1 skew-symmetric
     while (true) {
         p = skip_ws(p, end);
         if (p >= end) {
@@ -120,14 +272,19 @@ int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N, i
                 return SDDMM_PARSE_ERROR;
             }
             pattern = line.find("pattern") != std::string::npos;
+            if (line.find("skew-symmetric") != std::string::npos) symmetric = -1;
+            else if (line.find("symmetric") != std::string::npos || line.find("hermitian") != std::string::npos) symmetric = 1;
         }
         p = eol;
     }
 
     int64_t m = 0, n = 0, z = 0;
     const char *q = parse_i64(p, end, &m);
-    if (q) q = parse_i64(skip_blank_in_line(q, end), end, &n);
-    if (q) q = parse_i64(skip_blank_in_line(q, end), end, &z);
+    // the three sizes may sit on one line (Matrix Market) or on three (headerless bag-of-words
+    // "docword" files: documents, words, entries) -- the reference's other readers take both
+    // (`fp >> n_rows >> n_cols >> nnz`, other_ideas/our_work/sparse_dense_split/sddmm.cu:356)
+    if (q) q = parse_i64(skip_ws(q, end), end, &n);
+    if (q) q = parse_i64(skip_ws(q, end), end, &z);
     if (!q || m < 0 || n < 0 || z < 0) {
         set_err(errbuf, errbuf_len, "malformed size line (expected: rows cols nnz)");
         return SDDMM_PARSE_ERROR;
@@ -180,11 +337,39 @@ int sddmm_mtx_open(const char *path, sddmm_mtx_t *out, int64_t *M, int64_t *N, i
         mx->vals[(size_t)i] = v;
         p = t;
     }
-    if (M) *M = m;
-    if (N) *N = n;
-    if (nnz) *nnz = z;
+    {
+        const int st = finish_open(mx, flags, symmetric, errbuf, errbuf_len);
+        if (st != SDDMM_OK) { delete mx; return st; }
+    }
+    if (M) *M = mx->M;
+    if (N) *N = mx->N;
+    if (nnz) *nnz = mx->nnz;
     *out = mx;
     return SDDMM_OK;
+}
+
+int sddmm_coo_save_binary(const char *path, int64_t M, int64_t N, int64_t nnz, const int32_t *rows, const int32_t *cols,
+                          const float *vals)
+{
+    if (!path || M < 0 || N < 0 || nnz < 0 || (nnz > 0 && (!rows || !cols))) return SDDMM_INVALID_ARG;
+    FILE *f = std::fopen(path, "wb");
+    if (!f) return SDDMM_IO_ERROR;
+    BinHeader h;
+    std::memcpy(h.magic, BIN_MAGIC, 8);
+    h.version = 1;
+    h.flags = vals ? 1u : 0u;
+    h.M = M; h.N = N; h.nnz = nnz;
+    uint64_t sum = 0;
+    sum = checksum(sum, rows, sizeof(int32_t) * (size_t)nnz);
+    sum = checksum(sum, cols, sizeof(int32_t) * (size_t)nnz);
+    if (vals) sum = checksum(sum, vals, sizeof(float) * (size_t)nnz);
+    h.checksum = sum;
+    bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1;
+    ok = ok && (nnz == 0 || std::fwrite(rows, sizeof(int32_t), (size_t)nnz, f) == (size_t)nnz);
+    ok = ok && (nnz == 0 || std::fwrite(cols, sizeof(int32_t), (size_t)nnz, f) == (size_t)nnz);
+    ok = ok && (nnz == 0 || !vals || std::fwrite(vals, sizeof(float), (size_t)nnz, f) == (size_t)nnz);
+    ok = (std::fclose(f) == 0) && ok;
+    return ok ? SDDMM_OK : SDDMM_IO_ERROR;
 }
 
 int sddmm_mtx_read(sddmm_mtx_t f, int32_t *rows, int32_t *cols, float *vals)

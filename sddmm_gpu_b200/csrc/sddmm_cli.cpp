@@ -29,6 +29,11 @@
 //   --json FILE        write a small JSON report (ms, GFLOP/s, plan sizes)
 //   --write-mtx FILE   write the input matrix as Matrix Market (e.g. to hand a
 //                      generated matrix to another program)
+//   --save-bin FILE    write the input matrix in the library's binary form, which
+//                      loads without parsing (pass FILE as the input next time)
+//   --sort             an input that is not sorted by row is sorted by (row, col) on
+//                      the GPU instead of being refused
+//   --expand-symmetric a `symmetric` Matrix Market file stores one triangle: add the other
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -58,7 +63,7 @@ int main(int argc, char **argv)
 {
     if (argc < 5) {
         std::fprintf(stderr, "usage: %s input.mtx K tile_size_X tile_size_Y [--iters N] [--warmup N] "
-                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE]\n"
+                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE] [--save-bin FILE] [--sort] [--expand-symmetric]\n"
                              "       input may be gen:c1..c5 | gen:uniform:M:N:density | gen:zipf:M:N:nnz | "
                              "gen:rmat:scale:edge_factor | gen:band:M:half_width:g [:seed=S]\n", argv[0]);
         return 2;
@@ -69,7 +74,9 @@ int main(int argc, char **argv)
     const int col_tile = std::atoi(argv[4]);    // tile_sizeX in the reference
     int iters = 1, warmup = 0, device = 0;
     bool scale = true, gather = false;
-    const char *dump_p = nullptr, *json = nullptr, *write_mtx = nullptr;
+    const char *dump_p = nullptr, *json = nullptr, *write_mtx = nullptr, *save_bin = nullptr;
+    bool sort_input = false;
+    uint32_t open_flags = 0;
     for (int i = 5; i < argc; ++i) {
         std::string a = argv[i];
         auto need = [&](const char *name) -> const char * {
@@ -88,6 +95,9 @@ int main(int argc, char **argv)
         else if (a == "--dump-p") dump_p = need("--dump-p");
         else if (a == "--json") json = need("--json");
         else if (a == "--write-mtx") write_mtx = need("--write-mtx");
+        else if (a == "--save-bin") save_bin = need("--save-bin");
+        else if (a == "--sort") sort_input = true;
+        else if (a == "--expand-symmetric") open_flags |= SDDMM_MTX_EXPAND_SYMMETRIC;
         else {
             std::fprintf(stderr, "sddmm: unknown option %s\n", a.c_str());
             return 2;
@@ -100,7 +110,7 @@ int main(int argc, char **argv)
     char err[256] = "";
     const bool generated = std::strncmp(path, "gen:", 4) == 0;
     int st = generated ? sddmm_gen_open(path + 4, &f, &M, &N, &nnz, err, sizeof(err))
-                       : sddmm_mtx_open(path, &f, &M, &N, &nnz, err, sizeof(err));
+                       : sddmm_mtx_open_ex(path, open_flags, &f, &M, &N, &nnz, err, sizeof(err));
     if (st != SDDMM_OK) return die(generated ? "generating input" : "reading input", st, err);
     std::printf("\nMatrix info:  rows: %lld, cols: %lld, nnz: %lld\n", (long long)M, (long long)N, (long long)nnz);
     std::vector<int32_t> rows((size_t)nnz), cols((size_t)nnz);
@@ -108,12 +118,29 @@ int main(int argc, char **argv)
     st = sddmm_mtx_read(f, rows.data(), cols.data(), vals.data());
     if (st != SDDMM_OK) return die("reading input", st, "");
     std::printf("\nTilesize: X = %d, tilesize: Y = %d, TB: %d\n", col_tile, panel_rows, 256);
+    sddmm_handle_t h = nullptr;
+    st = sddmm_create(&h, device);
+    if (st != SDDMM_OK) return die("creating the engine", st, "");
+    if (!sddmm_coo_is_row_sorted(nnz, rows.data())) {
+        if (!sort_input) {
+            sddmm_destroy(h);
+            return die("input", SDDMM_UNSORTED_INPUT, "pass --sort, or convert it with sddmm_coo_sort_rows first");
+        }
+        st = sddmm_coo_sort_rows_gpu(h, &M, &N, nnz, rows.data(), cols.data(), vals.data(), 0);
+        if (st != SDDMM_OK) {
+            int rc = die("sorting the input", st, sddmm_last_error(h));
+            sddmm_destroy(h);
+            return rc;
+        }
+    }
     if (write_mtx) {
         st = sddmm_mtx_write(write_mtx, M, N, nnz, rows.data(), cols.data(), vals.data());
         if (st != SDDMM_OK) return die("writing the matrix", st, write_mtx);
     }
-    if (!sddmm_coo_is_row_sorted(nnz, rows.data()))
-        return die("input", SDDMM_UNSORTED_INPUT, "convert it with sddmm_coo_sort_rows first");
+    if (save_bin) {
+        st = sddmm_coo_save_binary(save_bin, M, N, nnz, rows.data(), cols.data(), vals.data());
+        if (st != SDDMM_OK) return die("writing the matrix", st, save_bin);
+    }
 
     std::vector<float> W((size_t)M * K), H((size_t)N * K), P((size_t)nnz);
     if (K > 0) {
@@ -121,9 +148,6 @@ int main(int argc, char **argv)
         initial(H, N, K);
     }
 
-    sddmm_handle_t h = nullptr;
-    st = sddmm_create(&h, device);
-    if (st != SDDMM_OK) return die("creating the engine", st, "");
     sddmm_plan_t plan = nullptr;
     st = sddmm_plan_coo(h, M, N, nnz, rows.data(), cols.data(), K, panel_rows, col_tile, 0, &plan);
     if (st != SDDMM_OK) {

@@ -322,6 +322,21 @@ def test_cli_prints_reference_lines_and_matches_oracle(tmp_path):
     assert (gM, gN) == (2048, 2048) and np.array_equal(g_rows, m2[2]) and np.array_equal(g_cols, m2[3])
     assert res.stdout.splitlines()[1] == f"Matrix info:  rows: 2048, cols: 2048, nnz: {g_rows.size}"
     assert_parity(np.fromfile(out, np.float32), g_rows, g_cols, oracle.cpu.initial(gM, 64), oracle.cpu.initial(gN, 64), g_vals)
+    # an input sorted by column: refused without --sort, sorted on the GPU with it; the binary form it saves
+    # loads back to the same result
+    order = np.lexsort((rows, cols))
+    col_sorted = str(tmp_path / "colsorted.mtx")
+    api.mtx_write(col_sorted, M, N, rows[order], cols[order], vals[order])
+    bad = subprocess.run([exe, col_sorted, str(K), "192", "50000"], capture_output=True, text=True)
+    assert bad.returncode != 0 and "not sorted by row" in bad.stderr
+    binf, out2 = str(tmp_path / "m.sddmm"), str(tmp_path / "p2.bin")
+    res = subprocess.run([exe, col_sorted, str(K), "192", "50000", "--sort", "--save-bin", binf, "--dump-p", out],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    assert_parity(np.fromfile(out, np.float32), rows, cols, oracle.cpu.initial(M, K), oracle.cpu.initial(N, K), vals)
+    res = subprocess.run([exe, binf, str(K), "192", "50000", "--dump-p", out2], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    assert np.array_equal(np.fromfile(out, np.float32), np.fromfile(out2, np.float32))
     # errors: non-zero exit code and one line on stderr instead of an assert
     bad = subprocess.run([exe, "gen:nosuch", "32", "192", "50000"], capture_output=True, text=True)
     assert bad.returncode != 0 and bad.stderr.startswith("sddmm: ")
@@ -477,3 +492,28 @@ def test_used_lines_and_row_upload(engine):
     with pytest.raises(api.SddmmError):
         engine.upload_rows(np.zeros((M, K), np.float32), torch.zeros((M, K), device="cuda"), plan.used_lines(0)[0], 1, K)
     plan.close()
+
+
+# ---- col-sorted -> row-sorted conversion on the GPU ------------------------------
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_gpu_coo_sort_equals_host_sort(engine, transpose):
+    import torch
+    rng = np.random.default_rng(11)
+    M, N, nnz = 900, 1300, 60000
+    rows = rng.integers(0, M, nnz).astype(np.int32)
+    cols = rng.integers(0, N, nnz).astype(np.int32)
+    rows[:2000], cols[:2000] = rows[2000:4000], cols[2000:4000]              # duplicates of (row, col) pairs
+    vals = rng.standard_normal(nnz).astype(np.float32)
+    order = np.lexsort((rows, cols))                                         # the reference's input: sorted by column
+    rows, cols, vals = rows[order].copy(), cols[order].copy(), vals[order].copy()
+    ref = api.coo_sort_rows(M, N, rows.copy(), cols.copy(), vals.copy(), transpose)
+    r, c, v = rows.copy(), cols.copy(), vals.copy()
+    m2, n2 = engine.coo_sort_rows(M, N, r, c, v, transpose)                  # host arrays, staged
+    assert (m2, n2) == (ref[0], ref[1])
+    assert np.array_equal(r, ref[2]) and np.array_equal(c, ref[3]) and np.array_equal(v, ref[4])
+    rd, cd, vd = (torch.from_numpy(x.copy()).cuda() for x in (rows, cols, vals))
+    engine.coo_sort_rows(M, N, rd, cd, vd, transpose)                        # device arrays, in place
+    torch.cuda.synchronize()
+    assert np.array_equal(rd.cpu().numpy(), ref[2]) and np.array_equal(cd.cpu().numpy(), ref[3])
+    assert np.array_equal(vd.cpu().numpy(), ref[4])

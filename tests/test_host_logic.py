@@ -232,3 +232,53 @@ def test_generators_are_deterministic_and_seeded():
     for bad in ("nosuch:1:2", "uniform:10:10:1.5", "rmat:40:2", "band:10:1:11", "uniform:10:10:0.1:seed=x"):
         with pytest.raises(api.SddmmError):
             api.gen_matrix(bad)
+
+
+# ---- formats around the loader ---------------------------------------------------
+
+def test_symmetric_files_expand_on_request(tmp_path):
+    path = tmp_path / "sym.mtx"
+    path.write_text("%%MatrixMarket matrix coordinate real symmetric\n% lower triangle\n4 4 4\n1 1 2.0\n3 1 -1.5\n4 2 7\n4 4 1\n")
+    M, N, rows, cols, vals = api.mtx_read(str(path))                       # as stored, like the reference
+    assert (M, N, rows.size) == (4, 4, 4)
+    M, N, rows, cols, vals = api.mtx_read(str(path), api.MTX_EXPAND_SYMMETRIC | api.MTX_SORT_ROWS)
+    got = sorted(zip(rows.tolist(), cols.tolist(), vals.tolist()))
+    assert got == [(0, 0, 2.0), (0, 2, -1.5), (1, 3, 7.0), (2, 0, -1.5), (3, 1, 7.0), (3, 3, 1.0)]
+    assert api.coo_is_row_sorted(rows)
+    skew = tmp_path / "skew.mtx"
+    skew.write_text("%%MatrixMarket matrix coordinate integer skew-symmetric\n3 3 1\n3 1 5\n")
+    _, _, rows, cols, vals = api.mtx_read(str(skew), api.MTX_EXPAND_SYMMETRIC | api.MTX_SORT_ROWS)
+    assert list(zip(rows.tolist(), cols.tolist(), vals.tolist())) == [(0, 2, -5.0), (2, 0, 5.0)]
+    rect = tmp_path / "rect.mtx"
+    rect.write_text("%%MatrixMarket matrix coordinate real symmetric\n3 4 1\n3 1 5\n")
+    with pytest.raises(api.SddmmError):
+        api.mtx_read(str(rect), api.MTX_EXPAND_SYMMETRIC)
+
+
+def test_docword_header_and_sorting_on_read(tmp_path):
+    # headerless bag-of-words triples: documents, words, entries on three lines, then doc word count
+    path = tmp_path / "docword.txt"
+    path.write_text("3\n5\n4\n2 5 3\n1 2 1\n3 1 9\n1 1 4\n")
+    M, N, rows, cols, vals = api.mtx_read(str(path), api.MTX_SORT_ROWS)
+    assert (M, N) == (3, 5)
+    assert list(zip(rows.tolist(), cols.tolist(), vals.tolist())) == [(0, 0, 4.0), (0, 1, 1.0), (1, 4, 3.0), (2, 0, 9.0)]
+
+
+def test_binary_matrix_round_trip_and_corruption(tmp_path):
+    M, N, rows, cols, vals = api.gen_matrix("rmat:10:6:seed=3")
+    path = str(tmp_path / "m.sddmm")
+    api.coo_save_binary(path, M, N, rows, cols, vals)
+    M2, N2, r2, c2, v2 = api.mtx_read(path)
+    assert (M2, N2) == (M, N) and np.array_equal(r2, rows) and np.array_equal(c2, cols) and np.array_equal(v2, vals)
+    api.coo_save_binary(path, M, N, rows, cols, None)                       # pattern only: values read back as 1
+    _, _, r3, c3, v3 = api.mtx_read(path)
+    assert np.array_equal(r3, rows) and np.all(v3 == 1.0)
+    api.coo_save_binary(path, M, N, rows, cols, vals)
+    raw = bytearray(open(path, "rb").read())
+    raw[48 + 4 * (rows.size // 2)] ^= 0x01                                   # flip one bit of a row index
+    open(path, "wb").write(raw)
+    with pytest.raises(api.SddmmError):
+        api.mtx_read(path)
+    open(path, "wb").write(raw[:100])
+    with pytest.raises(api.SddmmError):
+        api.mtx_read(path)
