@@ -693,6 +693,41 @@ __global__ void fill_dense_kernel(const unsigned long long *__restrict__ keys_s,
         }
     }
 }
+// Row masks and first-nonzero indices of every dense cell (one CTA per cell, grid-stride), and whether
+// the cell qualifies for the row-mask form: inside every row the list entries (input order) must have
+// consecutive input indices and ascending columns.
+__global__ void cell_row_masks_kernel(DenseCell *cells, int64_t n_cells, const int32_t *__restrict__ idx,
+                                      const uint16_t *__restrict__ rc, unsigned long long *row_mask, int32_t *row_base,
+                                      unsigned long long *n_mask_cells)
+{
+    __shared__ int bad;
+    for (int64_t cell = blockIdx.x; cell < n_cells; cell += gridDim.x) {
+        if (threadIdx.x == 0) bad = 0;
+        __syncthreads();
+        const DenseCell dc = cells[cell];
+        const int32_t *ci = idx + dc.offset;
+        const uint16_t *cr = rc + dc.offset;
+        unsigned long long *mk = row_mask + cell * DENSE_CELL_ROWS;
+        int32_t *bs = row_base + cell * DENSE_CELL_ROWS;
+        for (int t = threadIdx.x; t < dc.count; t += blockDim.x) {
+            const unsigned code = cr[t];
+            const int r = code >> 8, c = code & 255u;
+            atomicOr(mk + r, 1ull << c);
+            atomicMin(bs + r, ci[t]);
+            if (t > 0) {
+                const unsigned prev = cr[t - 1];
+                if ((prev >> 8) == (unsigned)r && (ci[t] != ci[t - 1] + 1 || (int)(prev & 255u) >= c)) bad = 1;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && !bad) {
+            cells[cell].cls = dc.cls | 0x100;
+            atomicAdd(n_mask_cells, 1ull);
+        }
+        __syncthreads();
+    }
+}
+
 struct NotDense {
     const unsigned char *is_dense;
     __device__ __forceinline__ bool operator()(int j) const { return is_dense[j] == 0; }
@@ -703,10 +738,11 @@ struct NotDense {
 void DensePlan::release()
 {
     cudaFree(cells); cudaFree(idx); cudaFree(rc); cudaFree(rows_s); cudaFree(cols_s); cudaFree(perm_s);
-    cudaFree(dense_rows); cudaFree(dense_cols);
+    cudaFree(dense_rows); cudaFree(dense_cols); cudaFree(row_mask); cudaFree(row_base);
     cells = nullptr; idx = nullptr; rc = nullptr; rows_s = cols_s = perm_s = nullptr;
     dense_rows = dense_cols = nullptr;
-    n_cells = n_dense_nnz = n_sparse = n_dense_rows = n_dense_cols = 0;
+    row_mask = nullptr; row_base = nullptr;
+    n_cells = n_dense_nnz = n_sparse = n_dense_rows = n_dense_cols = n_mask_cells = 0;
 }
 
 cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, const int64_t *d_row_ptr, int64_t nnz,
@@ -826,6 +862,24 @@ cudaError_t build_dense_cells(const int32_t *d_rows, const int32_t *d_cols, cons
                                                             d_rows, d_cols, row_vid, col_vid, nnz, geo, out->cells,
                                                             out->idx, out->rc, (unsigned char *)flags.ptr);
         CK(cudaGetLastError());
+        // row-mask form of the cells that allow it
+        {
+            const size_t lines_n = (size_t)n_dense_cells * DENSE_CELL_ROWS;
+            CK(cudaMalloc(&out->row_mask, sizeof(unsigned long long) * lines_n));
+            CK(cudaMalloc(&out->row_base, sizeof(int32_t) * lines_n));
+            CK(cudaMemsetAsync(out->row_mask, 0, sizeof(unsigned long long) * lines_n, stream));
+            CK(cudaMemsetAsync(out->row_base, 0x7f, sizeof(int32_t) * lines_n, stream));
+            Scratch cnt;
+            CK(cnt.reserve(sizeof(unsigned long long)));
+            CK(cudaMemsetAsync(cnt.ptr, 0, sizeof(unsigned long long), stream));
+            cell_row_masks_kernel<<<grid_for((int64_t)n_dense_cells * TPB), TPB, 0, stream>>>(
+                out->cells, n_dense_cells, out->idx, out->rc, out->row_mask, out->row_base, (unsigned long long *)cnt.ptr);
+            CK(cudaGetLastError());
+            unsigned long long n_mask = 0;
+            CK(cudaMemcpyAsync(&n_mask, cnt.ptr, sizeof(n_mask), cudaMemcpyDeviceToHost, stream));
+            CK(cudaStreamSynchronize(stream));
+            out->n_mask_cells = (int64_t)n_mask;
+        }
         const int64_t n_sparse = nnz - n_dense_nnz;
         if (n_sparse > 0) {
             CK(cudaMalloc(&out->perm_s, sizeof(int32_t) * (size_t)n_sparse));

@@ -85,6 +85,13 @@ struct DensePlan {
     int64_t n_cells = 0;
     int32_t *idx = nullptr;       // input index of every dense-cell nonzero, grouped by cell, row-major inside
     uint16_t *rc = nullptr;       // (row - row0) << 8 | (col - col0)
+    // Row-mask form of a cell (DenseCell::cls bit 8 set): per cell row a 64-bit column mask and the
+    // input index of the row's first nonzero inside the cell.  Valid for cells in which the nonzeros of
+    // every row are consecutive in the input with ascending columns (any (row, col)-sorted input, for
+    // cells over a contiguous column range); such a cell's nonzeros need no per-nonzero list.
+    unsigned long long *row_mask = nullptr;  // [n_cells][DENSE_CELL_ROWS]
+    int32_t *row_base = nullptr;             // [n_cells][DENSE_CELL_ROWS]
+    int64_t n_mask_cells = 0;
     int64_t n_dense_nnz = 0;
     int32_t *rows_s = nullptr, *cols_s = nullptr, *perm_s = nullptr;  // remainder: indices and input positions
     int64_t n_sparse = 0;

@@ -86,8 +86,10 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
 // Dense-cell kernel: every dense cell is computed as the 128 x 64 block
 // W[rows] * H[cols]^T -- fp32 FMAs, or (tensor) 3xTF32 on the tensor cores -- then
 // the cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).
+// Cells whose cls has bit 8 set are in row-mask form (row_mask / row_base, see DensePlan) and
+// do not read idx / rc.
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
-                               const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
+                               const unsigned long long *row_mask, const int32_t *row_base, const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream);
 

@@ -613,7 +613,8 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (!forced && !tiled_out && p->dense.n_cells > 0) {
         // locally dense plan: dense cells as small dense products, the rest gathered
-        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.dense_rows,
+        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
+                                       p->dense.row_base, p->dense.dense_rows,
                                        p->dense.n_dense_rows, p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP,
                                        p->M, p->N, p->K, h->dense_tensor, h->sm_count, s));
         if (p->dense.n_sparse > 0) {

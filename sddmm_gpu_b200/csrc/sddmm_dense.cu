@@ -38,7 +38,7 @@ constexpr int DR = DENSE_CELL_ROWS;  // 128
 constexpr int DC = DENSE_CELL_COLS;  // 64
 constexpr int KC = 64;               // K chunk staged at a time
 constexpr int KS = KC + 4;           // row stride of the staged operands (floats): 16-byte aligned rows, banks spread
-constexpr int CT_STRIDE = DC + 1;
+constexpr int CT_STRIDE = DC + 8;  // 72: the tensor path parks its fragments with conflict-free 64-bit stores
 constexpr int STAGE_FLOATS = (DR + DC) * KS;
 constexpr int BLOCK_FLOATS = DR * CT_STRIDE;  // the finished block; aliases the staging area
 constexpr int SMEM_FLOATS = STAGE_FLOATS > BLOCK_FLOATS ? STAGE_FLOATS : BLOCK_FLOATS;
@@ -78,7 +78,8 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 template <bool TENSOR>
 __global__ void __launch_bounds__(256, 3)
 sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const int32_t *__restrict__ idx,
-                   const uint16_t *__restrict__ rc, const int32_t *__restrict__ dense_rows, int64_t n_dense_rows,
+                   const uint16_t *__restrict__ rc, const unsigned long long *__restrict__ row_mask,
+                   const int32_t *__restrict__ row_base, const int32_t *__restrict__ dense_rows, int64_t n_dense_rows,
                    const int32_t *__restrict__ dense_cols, int64_t n_dense_cols, const float *__restrict__ sval,
                    const float *__restrict__ W, const float *__restrict__ H, float *__restrict__ P, int64_t M,
                    int64_t N, int K)
@@ -96,7 +97,9 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
     const int tx = tid & 15;
 
     for (int64_t cell = blockIdx.x; cell < n_cells; cell += gridDim.x) {
-        const DenseCell dc = cells[cell];
+        DenseCell dc = cells[cell];
+        const bool masked = (dc.cls & 0x100) != 0;  // row-mask form: no per-nonzero list
+        dc.cls &= 0xff;
         float acc[8][4];  // FMA path: [row i][col j]; tensor path: [m-tile*4 + n-tile][fragment register]
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -135,15 +138,9 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
                 const int fr = lane >> 2, fk = lane & 3;
 #pragma unroll 2
                 for (int kk = 0; kk < KC; kk += 8) {
-                    uint32_t a_hi[2][4], a_lo[2][4], b_hi[4][2], b_lo[4][2];
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        const float *p = Ws + (wr * 32 + mt * 16 + fr) * KS + kk + fk;
-                        split_tf32(p[0], a_hi[mt][0], a_lo[mt][0]);
-                        split_tf32(p[8 * KS], a_hi[mt][1], a_lo[mt][1]);
-                        split_tf32(p[4], a_hi[mt][2], a_lo[mt][2]);
-                        split_tf32(p[8 * KS + 4], a_hi[mt][3], a_lo[mt][3]);
-                    }
+                    // B fragments of the four n8 tiles first, then one m16 tile of A at a time: 24 split
+                    // operands live at once instead of 32, which keeps the kernel inside 80 registers
+                    uint32_t b_hi[4][2], b_lo[4][2];
 #pragma unroll
                     for (int nt = 0; nt < 4; ++nt) {
                         const float *p = Hs + (wc * 32 + nt * 8 + fr) * KS + kk + fk;
@@ -151,13 +148,20 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
                         split_tf32(p[4], b_hi[nt][1], b_lo[nt][1]);
                     }
 #pragma unroll
-                    for (int mt = 0; mt < 2; ++mt)
+                    for (int mt = 0; mt < 2; ++mt) {
+                        uint32_t a_hi[4], a_lo[4];
+                        const float *p = Ws + (wr * 32 + mt * 16 + fr) * KS + kk + fk;
+                        split_tf32(p[0], a_hi[0], a_lo[0]);
+                        split_tf32(p[8 * KS], a_hi[1], a_lo[1]);
+                        split_tf32(p[4], a_hi[2], a_lo[2]);
+                        split_tf32(p[8 * KS + 4], a_hi[3], a_lo[3]);
 #pragma unroll
                         for (int nt = 0; nt < 4; ++nt) {
-                            mma_tf32(acc[mt * 4 + nt], a_lo[mt], b_hi[nt]);
-                            mma_tf32(acc[mt * 4 + nt], a_hi[mt], b_lo[nt]);
-                            mma_tf32(acc[mt * 4 + nt], a_hi[mt], b_hi[nt]);
+                            mma_tf32(acc[mt * 4 + nt], a_lo, b_hi[nt]);
+                            mma_tf32(acc[mt * 4 + nt], a_hi, b_lo[nt]);
+                            mma_tf32(acc[mt * 4 + nt], a_hi, b_hi[nt]);
                         }
+                    }
                 }
             } else {
 #pragma unroll 2
@@ -189,10 +193,8 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const int r = wr * 32 + mt * 16 + (lane >> 2), c = wc * 32 + nt * 8 + (lane & 3) * 2;
-                    Ct[r * CT_STRIDE + c] = acc[mt * 4 + nt][0];
-                    Ct[r * CT_STRIDE + c + 1] = acc[mt * 4 + nt][1];
-                    Ct[(r + 8) * CT_STRIDE + c] = acc[mt * 4 + nt][2];
-                    Ct[(r + 8) * CT_STRIDE + c + 1] = acc[mt * 4 + nt][3];
+                    *reinterpret_cast<float2 *>(Ct + r * CT_STRIDE + c) = make_float2(acc[mt * 4 + nt][0], acc[mt * 4 + nt][1]);
+                    *reinterpret_cast<float2 *>(Ct + (r + 8) * CT_STRIDE + c) = make_float2(acc[mt * 4 + nt][2], acc[mt * 4 + nt][3]);
                 }
         } else {
 #pragma unroll
@@ -201,6 +203,45 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
                 for (int j = 0; j < 4; ++j) Ct[(ty + 16 * i) * CT_STRIDE + tx + 16 * j] = acc[i][j];
         }
         __syncthreads();
+        if (masked) {
+            // Row r of the cell holds the columns of mask[r]; its nonzeros are consecutive in the input from
+            // base[r] on, in column order, so the one in column c sits at base[r] + popc(mask[r] below bit c).
+            // A warp takes four rows at a time, lane l the columns l and l + 32: the S loads and the P stores of
+            // a row are one or two contiguous runs.
+            const unsigned long long *cm = row_mask + cell * DR;
+            const int32_t *cb = row_base + cell * DR;
+            const int lane = tid & 31, warp = tid >> 5;
+            const unsigned below = (1u << lane) - 1u;
+            for (int r0 = warp * 4; r0 < DR; r0 += 32) {
+                unsigned lo[4], hi[4];
+                int32_t base[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned long long m = __ldg(cm + r0 + u);
+                    lo[u] = (unsigned)m;
+                    hi[u] = (unsigned)(m >> 32);
+                    base[u] = __ldg(cb + r0 + u);
+                }
+                float s_lo[4], s_hi[4];
+                int32_t p_lo[4], p_hi[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    p_lo[u] = base[u] + __popc(lo[u] & below);
+                    p_hi[u] = base[u] + __popc(lo[u]) + __popc(hi[u] & below);
+                    s_lo[u] = s_hi[u] = 1.f;
+                    if (sval) {
+                        if ((lo[u] >> lane) & 1u) s_lo[u] = __ldcs(sval + p_lo[u]);
+                        if ((hi[u] >> lane) & 1u) s_hi[u] = __ldcs(sval + p_hi[u]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float *crow = Ct + (r0 + u) * CT_STRIDE;
+                    if ((lo[u] >> lane) & 1u) __stcs(P + p_lo[u], crow[lane] * s_lo[u]);
+                    if ((hi[u] >> lane) & 1u) __stcs(P + p_hi[u], crow[lane + 32] * s_hi[u]);
+                }
+            }
+        } else {
         const int32_t *cidx = idx + dc.offset;
         const uint16_t *crc = rc + dc.offset;
         int i = tid;
@@ -228,6 +269,7 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
             if (sval) v *= __ldg(sval + o);
             P[o] = v;
         }
+        }
         __syncthreads();  // the block is overwritten by the next cell's staging
     }
 }
@@ -235,7 +277,7 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
 }  // namespace
 
 cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
-                               const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
+                               const unsigned long long *row_mask, const int32_t *row_base, const int32_t *dense_rows, int64_t n_dense_rows, const int32_t *dense_cols,
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream)
 {
@@ -252,11 +294,13 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
     int64_t blocks = (int64_t)sm_count * 3;
     if (blocks > n_cells) blocks = n_cells;
     if (tensor)
-        sddmm_dense_kernel<true><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows,
-                                                                          dense_cols, n_dense_cols, sval, W, H, P, M, N, K);
+        sddmm_dense_kernel<true><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, row_mask, row_base,
+                                                                          dense_rows, n_dense_rows, dense_cols,
+                                                                          n_dense_cols, sval, W, H, P, M, N, K);
     else
-        sddmm_dense_kernel<false><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, dense_rows, n_dense_rows,
-                                                                           dense_cols, n_dense_cols, sval, W, H, P, M, N, K);
+        sddmm_dense_kernel<false><<<(unsigned)blocks, 256, smem, stream>>>(cells, n_cells, idx, rc, row_mask, row_base,
+                                                                           dense_rows, n_dense_rows, dense_cols,
+                                                                           n_dense_cols, sval, W, H, P, M, N, K);
     return cudaGetLastError();
 }
 

@@ -517,3 +517,24 @@ def test_gpu_coo_sort_equals_host_sort(engine, transpose):
     torch.cuda.synchronize()
     assert np.array_equal(rd.cpu().numpy(), ref[2]) and np.array_equal(cd.cpu().numpy(), ref[3])
     assert np.array_equal(vd.cpu().numpy(), ref[4])
+
+
+def test_dense_cells_with_columns_unsorted_inside_rows(engine):
+    # row-sorted input whose columns are shuffled inside every row: dense cells cannot use their row-mask
+    # form (a row's nonzeros are not in column order) and take the per-nonzero lists; results must not change
+    p = synth.to_numpy(synth.attention_mask(M=900, half_width=80, n_global=5, K=64, device="cpu"))
+    rng = np.random.default_rng(5)
+    rows, cols = p["rows"].copy(), p["cols"].copy()
+    vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+    P_sorted, info = run_plan(engine, p["M"], p["N"], rows, cols, p["W"], p["H"], vals)
+    assert info.n_dense_cells > 0
+    order = np.lexsort((rng.random(rows.shape[0]), rows))                    # random order inside each row
+    r2, c2, v2 = rows[order], cols[order], vals[order]
+    assert np.array_equal(r2, rows) and not np.array_equal(c2, cols)
+    P_shuffled, info2 = run_plan(engine, p["M"], p["N"], r2, c2, p["W"], p["H"], v2)
+    assert info2.n_dense_cells > 0
+    assert_parity(P_shuffled, r2, c2, p["W"], p["H"], v2)
+    inv = np.empty_like(order)
+    inv[order] = np.arange(order.size)
+    # the same values whatever the form (the gathered remainder may round differently with its neighbours)
+    assert np.allclose(P_shuffled[inv], P_sorted, rtol=1e-5, atol=1e-5)
