@@ -132,6 +132,7 @@ const float *mapped_host_ptr(const float *p)
         return nullptr;
     }
     if (a.type != cudaMemoryTypeHost || !a.devicePointer) return nullptr;
+    if (((uintptr_t)a.devicePointer & 15u) != 0) return nullptr;  // the row upload moves 16-byte vectors
     return static_cast<const float *>(a.devicePointer);
 }
 
@@ -460,7 +461,12 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
             PLAN_TRY(build_used_row_list(p->d_row_ptr, M, &p->d_used_rows, &p->n_used_rows, s));
             PLAN_TRY(build_used_col_list(p->d_cols, nnz, N, &p->d_used_cols, &p->n_used_cols, s));
             p->device_bytes += (int64_t)sizeof(int32_t) * (p->n_used_rows + p->n_used_cols);
-            std::vector<int32_t> used((size_t)p->n_used_rows);
+            std::vector<int32_t> used;
+            try {
+                used.resize((size_t)p->n_used_rows);
+            } catch (const std::bad_alloc &) {
+                PLAN_TRY(cudaErrorMemoryAllocation);
+            }
             PLAN_TRY(cudaMemcpyAsync(used.data(), p->d_used_rows, sizeof(int32_t) * used.size(), cudaMemcpyDeviceToHost, s));
             PLAN_TRY(cudaStreamSynchronize(s));  // also completes the copies of the chunks' first and last rows
             int64_t next_row = 0;  // first row of W no earlier chunk uploads
