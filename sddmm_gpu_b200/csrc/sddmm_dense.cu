@@ -58,13 +58,16 @@ __device__ __forceinline__ void cp_async_wait_all()
 
 // 3xTF32: an fp32 value x is split into hi = tf32(x) and lo = tf32(x - hi); the
 // product a*b is accumulated as lo_a*hi_b + hi_a*lo_b + hi_a*hi_b in fp32 by
-// three tensor-core MMAs, which keeps the error of the products at the 2^-21
+// three tensor-core MMAs, which keeps the error of the products at the 2^-19
 // level instead of TF32's 2^-11.
 __device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo)
 {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float rest = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+    // head = x with the 13 mantissa bits TF32 does not have cleared; tail = x - head, exact in fp32.
+    // The tensor core reads only the TF32 bits of an operand register, so the tail needs no conversion of
+    // its own: what it drops is below 2^-20 |x|.  Two instructions per operand instead of two conversions
+    // and a subtraction.
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
 {
