@@ -49,6 +49,8 @@ enum {
 /* ---- execute flags ------------------------------------------------------- */
 #define SDDMM_FLAG_ASYNC        0x1u /* return after enqueue on the handle's stream (device pointers only) */
 #define SDDMM_FLAG_TILED_ORDER  0x2u /* P in the plan's tiled order (what the reference's sddmm_GPU leaves in d_val, sddmm.cu:119) instead of input order */
+#define SDDMM_FLAG_H_TRANSPOSED  0x4u /* H is given K-major, H_t[t*N + c] -- the layout make_HTasH builds (util.h:68-73) -- and is transposed on the device first */
+#define SDDMM_FLAG_W_TRANSPOSED  0x8u /* W is given K-major, W_t[t*M + r] */
 #define SDDMM_FLAG_KERNEL_GATHER 0x10u /* force the planless gather kernel */
 #define SDDMM_FLAG_KERNEL_PANEL  0x20u /* force the TMA-staged row-panel kernel */
 #define SDDMM_FLAG_KERNEL_RING   0x40u /* force the shared-memory gather-ring kernels (K = 32, 64, 128, 256, 512 or 1024) */

@@ -62,6 +62,8 @@ class CpuOracle:
         L.oracle_sddmm_coo_f64.argtypes = [_i32p, _i32p, C.c_void_p, C.c_int64, _f32p, _f32p, C.c_int, _f64p, _f64p, C.c_int]
         L.oracle_initial.restype = None
         L.oracle_initial.argtypes = [_f32p, C.c_int64, C.c_int]
+        L.oracle_make_htash.restype = None
+        L.oracle_make_htash.argtypes = [_f32p, _f32p, C.c_int64, C.c_int]
         L.oracle_make_csr.restype = C.c_int64
         L.oracle_make_csr.argtypes = [_i32p, C.c_int64, C.c_int64, _i32p, _i32p]
         L.oracle_rewrite_matrix_1d.restype = C.c_int32
@@ -112,6 +114,14 @@ class CpuOracle:
         X = np.empty((n, k), np.float32)
         self.lib.oracle_initial(X, n, k)
         return X
+
+    def make_htash(self, H):
+        """K-major copy of an (n, k) operand: the reference's make_HTasH."""
+        H = _f32(H)
+        n, k = H.shape
+        Ht = np.empty((k, n), np.float32)
+        self.lib.oracle_make_htash(H, Ht, n, k)
+        return Ht
 
     def make_csr(self, rows, n_rows):
         rows = _i32(rows)
@@ -181,6 +191,9 @@ class RefChecker:
         L.ref_sddmm_cpu_csr.argtypes = [_i32p, _i32p, _f32p, C.c_long, C.c_long, C.c_long, _f32p, _f32p, C.c_int, _f32p]
         L.ref_initial.restype = None
         L.ref_initial.argtypes = [_f32p, C.c_long, C.c_int]
+        if hasattr(L, "ref_make_htash"):
+            L.ref_make_htash.restype = None
+            L.ref_make_htash.argtypes = [_f32p, _f32p, C.c_long, C.c_int]
         L.ref_make_csr.restype = None
         L.ref_make_csr.argtypes = [_i32p, C.c_long, C.c_long, _i32p, _i32p]
         L.ref_rewrite_matrix_1d.restype = C.c_int
@@ -221,6 +234,13 @@ class RefChecker:
         X = np.empty((n, k), np.float32)
         self.lib.ref_initial(X, n, k)
         return X
+
+    def make_htash(self, H):
+        H = _f32(H)
+        n, k = H.shape
+        Ht = np.empty((k, n), np.float32)
+        self.lib.ref_make_htash(H, Ht, n, k)
+        return Ht
 
     def make_csr(self, rows, n_rows):
         rows = _i32(rows)

@@ -99,6 +99,14 @@ void ref_sddmm_cpu_csr(int *row_ptr, int *cols, float *vals, long nnz, long n_ro
     sddmm_CPU_CSR(row_ptr, cols, vals, Wv, Hv, P, S);
 }
 
+/* make_HTasH (util.h:68-73). */
+void ref_make_htash(const float *H, float *H_t, long n, int K)
+{
+    vector<float> h(H, H + n * (long)K), ht(n * (long)K);
+    make_HTasH(h, ht, (int)n, K);
+    memcpy(H_t, ht.data(), sizeof(float) * ht.size());
+}
+
 /* initial (util.h:75-81). */
 void ref_initial(float *X, long n, int K)
 {

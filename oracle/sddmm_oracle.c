@@ -149,6 +149,14 @@ ORACLE_API void oracle_sddmm_coo_f64(const int32_t *row_ind, const int32_t *col_
     }
 }
 
+/* HiPC18/src/util.h:68-73 (make_HTasH): H_t[t*n + r] = H[r*k + t], the K-major copy of an n x k operand. */
+ORACLE_API void oracle_make_htash(const float *H, float *H_t, int64_t n, int k)
+{
+    for (int64_t r = 0; r < n; ++r)
+        for (int64_t t = 0; t < k; ++t)
+            H_t[t * n + r] = H[r * k + t];
+}
+
 /* HiPC18/src/util.h:75-81 (initial): srand48(0) then X[r*k+t] = 0.1*drand48(). */
 ORACLE_API void oracle_initial(float *X, int64_t n, int k)
 {

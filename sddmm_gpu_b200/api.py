@@ -20,6 +20,8 @@ OK, INVALID_ARG, UNSORTED_INPUT, INDEX_OUT_OF_RANGE, K_UNSUPPORTED, CUDA_ERROR, 
 
 FLAG_ASYNC = 0x1
 FLAG_TILED_ORDER = 0x2
+FLAG_H_TRANSPOSED = 0x4
+FLAG_W_TRANSPOSED = 0x8
 FLAG_KERNEL_GATHER = 0x10
 FLAG_KERNEL_PANEL = 0x20
 FLAG_KERNEL_RING = 0x40

@@ -68,6 +68,9 @@ cudaError_t launch_panel(const WorkItem *items, int64_t n_items, const int32_t *
                          const PanelConfig &cfg, int sm_count, int *dev_status,
                          cudaStream_t stream);
 
+// dst[r*K + t] = src[t*n + r]: a K-major operand (K x n) into the row-major layout (n x K) the kernels read.
+cudaError_t launch_transpose_operand(const float *src_kmajor, float *dst_rowmajor, int64_t n, int K, cudaStream_t stream);
+
 // Copies the listed rows (K floats each) of a row-major array in mapped, page-locked
 // host memory to the same rows of a device array; the GPU reads the host memory.
 cudaError_t launch_upload_rows(const float *mapped_host, float *dev, const int32_t *d_row_list, int64_t n_rows, int K,

@@ -76,6 +76,7 @@ struct sddmm_plan_s {
     int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
     // staging for host operands (allocated on first use)
     float *d_W = nullptr, *d_H = nullptr, *d_S = nullptr, *d_P = nullptr;
+    float *d_Wt = nullptr, *d_Ht = nullptr;  // device copies of K-major host operands, before their transposition
     int64_t device_bytes = 0;
     float plan_ms = 0.f, last_ms = -1.f;
     // chunks of the host-operand pipeline (0 = not pipelined): nonzeros
@@ -167,6 +168,8 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_item_rows_s);
     cudaFree(p->d_used_rows);
     cudaFree(p->d_used_cols);
+    cudaFree(p->d_Wt);
+    cudaFree(p->d_Ht);
     cudaFree(p->d_W);
     cudaFree(p->d_H);
     cudaFree(p->d_S);
@@ -530,13 +533,27 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     const size_t nbytes = sizeof(float) * (size_t)p->nnz;
     // W in host memory and a plain ring-kernel plan: upload W (and S) chunk by chunk
     // and let every chunk's kernel and download run behind the later uploads
+    const bool w_t = (flags & SDDMM_FLAG_W_TRANSPOSED) != 0, h_t = (flags & SDDMM_FLAG_H_TRANSPOSED) != 0;
     const bool pipelined = h->pipeline && p->n_pipe > 0 && !w_dev && use_ring && !tiled_out && !p->d_perm &&
-                           p->dense.n_cells == 0;
+                           p->dense.n_cells == 0 && !w_t && !h_t;
     // page-locked, mapped host arrays are read row by row by the GPU: only the rows a nonzero touches travel
     const float *W_mapped = (pipelined && h->sparse_upload) ? mapped_host_ptr(W) : nullptr;
     const float *H_mapped = (pipelined && h->sparse_upload && !h_dev) ? mapped_host_ptr(H) : nullptr;
     p->last_h2d_bytes = p->last_d2h_bytes = 0;
-    if (!h_dev) {
+    // K-major operands (the layout make_HTasH builds, util.h:68-73): brought to the device if need be and
+    // transposed there into the plan's row-major staging copy
+    if (h_t) {
+        const float *src = H;
+        if (!h_dev) {
+            if (!p->d_Ht) CUDA_TRY(h, dev_alloc(p, &p->d_Ht, (size_t)p->N * p->K));
+            CUDA_TRY(h, cudaMemcpyAsync(p->d_Ht, H, hbytes, cudaMemcpyHostToDevice, s));
+            p->last_h2d_bytes += (int64_t)hbytes;
+            src = p->d_Ht;
+        }
+        if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
+        CUDA_TRY(h, launch_transpose_operand(src, p->d_H, p->N, p->K, s));
+        dH = p->d_H;
+    } else if (!h_dev) {
         if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
         if (H_mapped) {
             CUDA_TRY(h, launch_upload_rows(H_mapped, p->d_H, p->d_used_cols, p->n_used_cols, p->K, h->upload_ctas, s));
@@ -547,7 +564,18 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         }
         dH = p->d_H;
     }
-    if (!w_dev) {
+    if (w_t) {
+        const float *src = W;
+        if (!w_dev) {
+            if (!p->d_Wt) CUDA_TRY(h, dev_alloc(p, &p->d_Wt, (size_t)p->M * p->K));
+            CUDA_TRY(h, cudaMemcpyAsync(p->d_Wt, W, wbytes, cudaMemcpyHostToDevice, s));
+            p->last_h2d_bytes += (int64_t)wbytes;
+            src = p->d_Wt;
+        }
+        if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
+        CUDA_TRY(h, launch_transpose_operand(src, p->d_W, p->M, p->K, s));
+        dW = p->d_W;
+    } else if (!w_dev) {
         if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
         if (!pipelined) {
             CUDA_TRY(h, cudaMemcpyAsync(p->d_W, W, wbytes, cudaMemcpyHostToDevice, s));

@@ -46,7 +46,44 @@ upload_rows_kernel(const char *__restrict__ src, char *__restrict__ dst, const i
     }
 }
 
+// 32 x 32 tiles through shared memory: coalesced reads along n, coalesced writes along K.
+__global__ void __launch_bounds__(256)
+transpose_operand_kernel(const float *__restrict__ src, float *__restrict__ dst, int64_t n, int K)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+    const int64_t n_tiles_n = (n + 31) / 32;
+    const int64_t n_tiles = n_tiles_n * ((K + 31) / 32);
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t r0 = (t % n_tiles_n) * 32;
+        const int k0 = (int)(t / n_tiles_n) * 32;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int k = k0 + ty + j;
+            const int64_t r = r0 + tx;
+            tile[ty + j][tx] = (k < K && r < n) ? src[(int64_t)k * n + r] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int64_t r = r0 + ty + j;
+            const int k = k0 + tx;
+            if (r < n && k < K) dst[r * K + k] = tile[tx][ty + j];
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_transpose_operand(const float *src_kmajor, float *dst_rowmajor, int64_t n, int K, cudaStream_t stream)
+{
+    if (n == 0 || K == 0) return cudaSuccess;
+    const int64_t n_tiles = ((n + 31) / 32) * ((K + 31) / 32);
+    const unsigned grid = (unsigned)(n_tiles < 148 * 16 ? n_tiles : 148 * 16);
+    transpose_operand_kernel<<<grid, 256, 0, stream>>>(src_kmajor, dst_rowmajor, n, K);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_upload_rows(const float *mapped_host, float *dev, const int32_t *d_row_list, int64_t n_rows, int K,
                                int n_ctas, cudaStream_t stream)

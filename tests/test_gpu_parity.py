@@ -538,3 +538,32 @@ def test_dense_cells_with_columns_unsorted_inside_rows(engine):
     inv[order] = np.arange(order.size)
     # the same values whatever the form (the gathered remainder may round differently with its neighbours)
     assert np.allclose(P_shuffled[inv], P_sorted, rtol=1e-5, atol=1e-5)
+
+
+# ---- K-major operands (the layout the reference's make_HTasH builds) -------------
+
+@pytest.mark.parametrize("K", [32, 100, 256])
+def test_transposed_operands(engine, K):
+    import torch
+    rng = np.random.default_rng(K)
+    M, N = 700, 450
+    rows, cols = random_coo(rng, M, N, 9000, empty_rows=(0, 5, 699))
+    W = rng.standard_normal((M, K)).astype(np.float32)
+    H = rng.standard_normal((N, K)).astype(np.float32)
+    vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+    Wt, Ht = oracle.cpu.make_htash(W), oracle.cpu.make_htash(H)
+    P_ref, _ = run_plan(engine, M, N, rows, cols, W, H, vals)
+    assert_parity(P_ref, rows, cols, W, H, vals)
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    for w_t, h_t in ((False, True), (True, False), (True, True)):
+        flags = (api.FLAG_W_TRANSPOSED if w_t else 0) | (api.FLAG_H_TRANSPOSED if h_t else 0)
+        P = np.full(rows.shape[0], np.nan, np.float32)
+        plan.execute(Wt if w_t else W, Ht if h_t else H, P, vals, flags)           # host operands
+        assert np.array_equal(P, P_ref)
+        Wd = torch.from_numpy(np.ascontiguousarray(Wt if w_t else W)).cuda()
+        Hd = torch.from_numpy(np.ascontiguousarray(Ht if h_t else H)).cuda()
+        Pd = torch.full((rows.shape[0],), float("nan"), device="cuda")
+        plan.execute(Wd, Hd, Pd, torch.from_numpy(vals).cuda(), flags)              # device operands
+        torch.cuda.synchronize()
+        assert np.array_equal(Pd.cpu().numpy(), P_ref)
+    plan.close()

@@ -97,3 +97,12 @@ def test_make_csc_cuts():
     cols = np.array([0, 0, 1, 2, 2, 2, 3, 5, 5, 7], np.int32)
     cir, nir = oracle.cpu.make_csc_cuts(cols, 8, 2)
     assert nir.sum() == cols.size and len(cir) >= 2
+
+
+def test_make_htash_restatement():
+    rng = np.random.default_rng(8)
+    H = rng.standard_normal((37, 20)).astype(np.float32)
+    Ht = oracle.cpu.make_htash(H)
+    assert Ht.shape == (20, 37) and np.array_equal(Ht, H.T)
+    if oracle.ref is not None and hasattr(oracle.ref.lib, "ref_make_htash"):
+        assert np.array_equal(oracle.ref.make_htash(H), Ht)          # the reference's make_HTasH itself
