@@ -282,3 +282,22 @@ def test_binary_matrix_round_trip_and_corruption(tmp_path):
     open(path, "wb").write(raw[:100])
     with pytest.raises(api.SddmmError):
         api.mtx_read(path)
+
+
+def test_c_client_of_the_abi(tmp_path):
+    """A plain C99 program compiled against include/sddmm_b200.h and linked with the library."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else shutil.which("gcc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    libdir = os.path.join(root, "sddmm_gpu_b200", "csrc")
+    exe = str(tmp_path / "host_only")
+    build = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(root, "include"),
+                            os.path.join(root, "tests", "c_abi", "host_only.c"), "-o", exe, "-L", libdir, "-lsddmm_b200",
+                            "-Wl,-rpath," + libdir], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([exe], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "FAILED" not in run.stdout
