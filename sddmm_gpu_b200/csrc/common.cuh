@@ -96,6 +96,14 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
                                int64_t n_dense_cols, const float *sval, const float *W, const float *H, float *P,
                                int64_t M, int64_t N, int K, bool tensor, int sm_count, cudaStream_t stream);
 
+// The same dense cells on tcgen05: MMAs issued by one thread from shared-memory descriptors, accumulator in
+// tensor memory (3xTF32).  dev_status receives DEV_MBARRIER_TIMEOUT if a bounded wait gives up.
+cudaError_t launch_dense_cells_tc(const DenseCell *cells, int64_t n_cells, const int32_t *idx, const uint16_t *rc,
+                                  const unsigned long long *row_mask, const int32_t *row_base, const int32_t *dense_rows,
+                                  int64_t n_dense_rows, const int32_t *dense_cols, int64_t n_dense_cols, const float *sval,
+                                  const float *W, const float *H, float *P, int64_t M, int64_t N, int K, int sm_count,
+                                  int *dev_status, cudaStream_t stream);
+
 // Ring kernel for short rows (K = 32, 64, 128): the same per-warp rings filled with
 // 16-byte cp.async copies; reached through launch_ring.
 cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,

@@ -34,7 +34,8 @@ struct sddmm_handle_s {
     unsigned long long *d_work_counter = nullptr;  // dynamic work distribution of the ring kernel
     int *h_status = nullptr;  // pinned mirror
     std::string last_error;
-    bool dense_tensor = true;  // dense cells on the tensor cores (3xTF32); SDDMM_DENSE_TENSOR=0 selects fp32 FMA
+    // dense cells: 0 = fp32 FMA, 1 = 3xTF32 on mma.sync, 2 = 3xTF32 on tcgen05 / tensor memory (SDDMM_DENSE_TENSOR)
+    int dense_mode = 1;
     // pipelined execution with host operands: compute and download streams, one
     // "uploaded" and one "computed" event per chunk (created on first use)
     cudaStream_t pipe_compute = nullptr, pipe_download = nullptr;
@@ -264,7 +265,10 @@ int sddmm_create(sddmm_handle_t *out, int device)
     }
     *h->h_status = DEV_OK;
     h->stream = h->own_stream;
-    if (const char *env = std::getenv("SDDMM_DENSE_TENSOR")) h->dense_tensor = std::atoi(env) != 0;
+    if (const char *env = std::getenv("SDDMM_DENSE_TENSOR")) {
+        const int v = std::atoi(env);
+        if (v >= 0 && v <= 2) h->dense_mode = v;
+    }
     if (const char *env = std::getenv("SDDMM_PIPELINE")) h->pipeline = std::atoi(env) != 0;
     if (const char *env = std::getenv("SDDMM_SPARSE_UPLOAD")) h->sparse_upload = std::atoi(env) != 0;
     h->upload_ctas = h->sm_count / 2 > 0 ? h->sm_count / 2 : 1;
@@ -647,10 +651,16 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (!forced && !tiled_out && p->dense.n_cells > 0) {
         // locally dense plan: dense cells as small dense products, the rest gathered
-        CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
-                                       p->dense.row_base, p->dense.dense_rows,
-                                       p->dense.n_dense_rows, p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP,
-                                       p->M, p->N, p->K, h->dense_tensor, h->sm_count, s));
+        if (h->dense_mode == 2)
+            CUDA_TRY(h, launch_dense_cells_tc(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
+                                              p->dense.row_base, p->dense.dense_rows, p->dense.n_dense_rows,
+                                              p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP, p->M, p->N, p->K,
+                                              h->sm_count, h->d_status, s));
+        else
+            CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
+                                           p->dense.row_base, p->dense.dense_rows, p->dense.n_dense_rows,
+                                           p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP, p->M, p->N, p->K,
+                                           h->dense_mode == 1, h->sm_count, s));
         if (p->dense.n_sparse > 0) {
             if (ring_supports(p->K))
                 CUDA_TRY(h, launch_ring(p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP, p->dense.n_sparse,

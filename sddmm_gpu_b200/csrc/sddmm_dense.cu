@@ -29,6 +29,7 @@
 #include <stdint.h>
 
 #include "common.cuh"
+#include "dense_pick.cuh"
 
 namespace sddmm {
 
@@ -206,73 +207,7 @@ sddmm_dense_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const i
                 for (int j = 0; j < 4; ++j) Ct[(ty + 16 * i) * CT_STRIDE + tx + 16 * j] = acc[i][j];
         }
         __syncthreads();
-        if (masked) {
-            // Row r of the cell holds the columns of mask[r]; its nonzeros are consecutive in the input from
-            // base[r] on, in column order, so the one in column c sits at base[r] + popc(mask[r] below bit c).
-            // A warp takes four rows at a time, lane l the columns l and l + 32: the S loads and the P stores of
-            // a row are one or two contiguous runs.
-            const unsigned long long *cm = row_mask + cell * DR;
-            const int32_t *cb = row_base + cell * DR;
-            const int lane = tid & 31, warp = tid >> 5;
-            const unsigned below = (1u << lane) - 1u;
-            for (int r0 = warp * 4; r0 < DR; r0 += 32) {
-                unsigned lo[4], hi[4];
-                int32_t base[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const unsigned long long m = __ldg(cm + r0 + u);
-                    lo[u] = (unsigned)m;
-                    hi[u] = (unsigned)(m >> 32);
-                    base[u] = __ldg(cb + r0 + u);
-                }
-                float s_lo[4], s_hi[4];
-                int32_t p_lo[4], p_hi[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    p_lo[u] = base[u] + __popc(lo[u] & below);
-                    p_hi[u] = base[u] + __popc(lo[u]) + __popc(hi[u] & below);
-                    s_lo[u] = s_hi[u] = 1.f;
-                    if (sval) {
-                        if ((lo[u] >> lane) & 1u) s_lo[u] = __ldcs(sval + p_lo[u]);
-                        if ((hi[u] >> lane) & 1u) s_hi[u] = __ldcs(sval + p_hi[u]);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float *crow = Ct + (r0 + u) * CT_STRIDE;
-                    if ((lo[u] >> lane) & 1u) __stcs(P + p_lo[u], crow[lane] * s_lo[u]);
-                    if ((hi[u] >> lane) & 1u) __stcs(P + p_hi[u], crow[lane + 32] * s_hi[u]);
-                }
-            }
-        } else {
-        const int32_t *cidx = idx + dc.offset;
-        const uint16_t *crc = rc + dc.offset;
-        int i = tid;
-        for (; i + 768 < dc.count; i += 1024) {  // four independent nonzeros per thread and trip
-            unsigned code[4];
-            int32_t o[4];
-            float v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                code[u] = __ldcs(crc + i + u * 256);
-                o[u] = __ldcs(cidx + i + u * 256);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                v[u] = Ct[(code[u] >> 8) * CT_STRIDE + (code[u] & 255u)];
-                if (sval) v[u] *= __ldg(sval + o[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) P[o[u]] = v[u];
-        }
-        for (; i < dc.count; i += 256) {
-            const unsigned code = crc[i];
-            const int32_t o = cidx[i];
-            float v = Ct[(code >> 8) * CT_STRIDE + (code & 255u)];
-            if (sval) v *= __ldg(sval + o);
-            P[o] = v;
-        }
-        }
+        pick_block(Ct, CT_STRIDE, dc, masked, cell, tid, idx, rc, row_mask, row_base, sval, P);
         __syncthreads();  // the block is overwritten by the next cell's staging
     }
 }

@@ -567,3 +567,28 @@ def test_transposed_operands(engine, K):
         torch.cuda.synchronize()
         assert np.array_equal(Pd.cpu().numpy(), P_ref)
     plan.close()
+
+
+# ---- dense cells on tcgen05 / tensor memory ---------------------------------------
+
+@pytest.mark.parametrize("K", [16, 64, 100, 256])
+def test_dense_cells_on_tcgen05(monkeypatch, K):
+    monkeypatch.setenv("SDDMM_DENSE_TENSOR", "2")
+    h = api.Handle(0)
+    p = synth.to_numpy(synth.attention_mask(M=1100, half_width=96, n_global=7, K=K, device="cpu"))
+    rng = np.random.default_rng(K)
+    vals = rng.standard_normal(p["rows"].shape[0]).astype(np.float32)
+    for sv in (vals, None):
+        P, info = run_plan(h, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], sv, 0)
+        assert info.n_dense_cells > 0 and 0 < info.n_dense_nnz <= info.nnz
+        assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], sv)
+    # a plan reused for several calls: tensor memory is allocated and released by every launch
+    plan = h.plan_coo(p["M"], p["N"], p["rows"], p["cols"], K)
+    outs = []
+    for _ in range(3):
+        P = np.full(p["rows"].shape[0], np.nan, np.float32)
+        plan.execute(p["W"], p["H"], P, vals)
+        outs.append(P)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    plan.close()
+    h.close()
