@@ -35,7 +35,7 @@ struct sddmm_handle_s {
     int *h_status = nullptr;  // pinned mirror
     std::string last_error;
     // dense cells: 0 = fp32 FMA, 1 = 3xTF32 on mma.sync, 2 = 3xTF32 on tcgen05 / tensor memory (SDDMM_DENSE_TENSOR)
-    int dense_mode = 1;
+    int dense_mode = 2;
     // pipelined execution with host operands: compute and download streams, one
     // "uploaded" and one "computed" event per chunk (created on first use)
     cudaStream_t pipe_compute = nullptr, pipe_download = nullptr;

@@ -569,11 +569,13 @@ def test_transposed_operands(engine, K):
     plan.close()
 
 
-# ---- dense cells on tcgen05 / tensor memory ---------------------------------------
+# ---- the three dense-cell kernels ---------------------------------------------------
 
+@pytest.mark.parametrize("mode", ["2", "1", "0"])
 @pytest.mark.parametrize("K", [16, 64, 100, 256])
-def test_dense_cells_on_tcgen05(monkeypatch, K):
-    monkeypatch.setenv("SDDMM_DENSE_TENSOR", "2")
+def test_dense_cell_variants(monkeypatch, K, mode):
+    # 2 = tcgen05 / tensor memory (the default), 1 = mma.sync, 0 = fp32 FMA
+    monkeypatch.setenv("SDDMM_DENSE_TENSOR", mode)
     h = api.Handle(0)
     p = synth.to_numpy(synth.attention_mask(M=1100, half_width=96, n_global=7, K=K, device="cpu"))
     rng = np.random.default_rng(K)
