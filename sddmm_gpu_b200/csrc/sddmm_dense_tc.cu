@@ -66,6 +66,15 @@ constexpr int MMA_WARP = N_PRODUCERS / 32, EPI_WARP0 = MMA_WARP + 1;
 constexpr int TC_THREADS = N_PRODUCERS + 32 + N_EPILOGUE;  // 800
 constexpr uint32_t TMEM_COLS = 2 * DC;  // two accumulators
 constexpr uint32_t LBO = 128, SBO = (KC / 4) * 128;
+// What the epilogue needs to know about a cell before its product is there: fetched into shared memory two
+// cells ahead.
+constexpr int META_SLOTS = 4;
+struct __align__(16) MetaSlot {
+    unsigned long long mask[DENSE_CELL_ROWS];  // columns held by each cell row
+    int32_t base[DENSE_CELL_ROWS];             // input index of each cell row's first nonzero
+    int32_t cls;                               // DenseCell::cls (class, row-mask flag)
+    int32_t pad[3];
+};
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4), version 1, no swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
@@ -131,17 +140,18 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
     extern __shared__ __align__(1024) unsigned char smem[];
     float *Ct = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES);
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ MetaSlot meta[META_SLOTS];
     __shared__ uint32_t tmem_holder;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], N_PRODUCERS);  // every producer thread arrives after its own stores
+            mbar_init(&full_bar[s], N_PRODUCERS / 32);  // one arrival per producer warp, after all its lanes' stores
             mbar_init(&empty_bar[s], 1);           // one tcgen05.commit
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);            // one tcgen05.commit
-            mbar_init(&acc_empty[b], N_EPILOGUE);  // every epilogue thread arrives after its tcgen05.ld
+            mbar_init(&acc_empty[b], N_EPILOGUE / 32);  // one arrival per epilogue warp, after its tcgen05.ld
         }
         mbar_fence_init();
     }
@@ -221,8 +231,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         };
         ok = issue() && issue();
         for (unsigned g = 0; g < total && ok; ++g) {
-            if (!issue()) { ok = false; break; }
-            asm volatile("cp.async.wait_group 2;" ::: "memory");  // this thread's copies of chunk g have landed
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's copies of chunk g have landed
             unsigned char *st = smem + (g % STAGES) * STAGE_BYTES;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -235,7 +244,10 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                 tail_store(*reinterpret_cast<const float4 *>(st + 2 * A_TILE_BYTES + off), st + 2 * A_TILE_BYTES + B_TILE_BYTES + off);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // my copies and stores -> visible to the tensor core
-            mbar_arrive(&full_bar[g % STAGES]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[g % STAGES]);
+            // only now the copies of chunk g + 2: they need the stage of chunk g - 1, whose MMAs ran meanwhile
+            if (!issue()) { ok = false; break; }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp == MMA_WARP) {
@@ -282,42 +294,59 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
     } else {
         // ---------------- epilogue ----------------
         // Sixteen warps.  Warp ew reads TMEM lanes 32 (warp % 4) .., columns 16 (ew / 4) .. + 16 of the finished
-        // block and parks them; it then picks the block's rows 8 ew .. 8 ew + 7.  Row masks and base indices of
-        // the next cell are fetched while the current one is picked, and a cell's S values are loaded before its
-        // accumulator is waited for, so that a cell costs no exposed round of memory latency of its own.
+        // block and parks them; it then picks the block's rows 8 ew .. 8 ew + 7.  What does not depend on the product
+        // runs ahead of it: a cell's row masks and base indices come into shared memory two cells early
+        // (cp.async), its S values into registers one cell early.
         const int et = tid - EPI_WARP0 * 32;  // 0 .. 511
         const int ew = et >> 5;               // epilogue warp 0 .. 15
         const int quarter = warp & 3, cgroup = ew >> 2;
         const int row = quarter * 32 + lane;
         const unsigned below = (1u << lane) - 1u;
-        unsigned n_acc = 0;
-        int64_t cell = blockIdx.x;
-        unsigned long long mk[8];
-        int32_t bs[8];
-        int cls_word = 0;
-        auto fetch_meta = [&](int64_t c) {
-            cls_word = cells[c].cls;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                mk[j] = __ldg(row_mask + c * DR + ew * 8 + j);
-                bs[j] = __ldg(row_base + c * DR + ew * 8 + j);
+        const int my_cells = (int)((n_cells - blockIdx.x + gridDim.x - 1) / gridDim.x);
+        // metadata of cell i of this CTA -> ring slot i % META_SLOTS, by 16-byte cp.async (97 threads take part)
+        auto fetch_meta = [&](int i) {
+            if (i < my_cells) {
+                const int64_t c = blockIdx.x + (int64_t)i * gridDim.x;
+                MetaSlot &m = meta[i % META_SLOTS];
+                if (et < 64) cp_async16_zfill(&m.mask[et * 2], row_mask + c * DR + et * 2, 16);
+                else if (et < 96) cp_async16_zfill(&m.base[(et - 64) * 4], row_base + c * DR + (et - 64) * 4, 16);
+                else if (et == 96)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(&m.cls)), "l"(&cells[c].cls) : "memory");
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        if (cell < n_cells) fetch_meta(cell);
-        for (; cell < n_cells; cell += gridDim.x) {
-            const bool masked = (cls_word & 0x100) != 0;
-            // S values of this warp's rows (row-mask form): lane l takes the columns l and l + 32 of a row; the
-            // nonzero in column c sits at base + popc(mask below bit c)
-            float s_lo[8], s_hi[8];
+        // S values of this warp's rows of cell i (row-mask form): lane l takes the columns l and l + 32 of a row; the
+        // nonzero in column c sits at base + popc(mask below bit c)
+        auto load_s = [&](int i, float (&s_lo)[8], float (&s_hi)[8]) {
+            const MetaSlot &m = meta[i % META_SLOTS];
+            const bool on = i < my_cells && (m.cls & 0x100) != 0 && sval != nullptr;
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const unsigned lo = (unsigned)mk[u], hi = (unsigned)(mk[u] >> 32);
                 s_lo[u] = s_hi[u] = 1.f;
-                if (masked && sval) {
-                    if ((lo >> lane) & 1u) s_lo[u] = __ldcs(sval + bs[u] + __popc(lo & below));
-                    if ((hi >> lane) & 1u) s_hi[u] = __ldcs(sval + bs[u] + __popc(lo) + __popc(hi & below));
+                if (on) {
+                    const unsigned long long mk = m.mask[ew * 8 + u];
+                    const unsigned lo = (unsigned)mk, hi = (unsigned)(mk >> 32);
+                    const int32_t bs = m.base[ew * 8 + u];
+                    if ((lo >> lane) & 1u) s_lo[u] = __ldcs(sval + bs + __popc(lo & below));
+                    if ((hi >> lane) & 1u) s_hi[u] = __ldcs(sval + bs + __popc(lo) + __popc(hi & below));
                 }
             }
+        };
+        fetch_meta(0);
+        fetch_meta(1);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        epilogue_sync();
+        float s_lo[8], s_hi[8];
+        load_s(0, s_lo, s_hi);
+        unsigned n_acc = 0;
+        for (int i = 0; i < my_cells; ++i) {
+            const int64_t cell = blockIdx.x + (int64_t)i * gridDim.x;
+            const MetaSlot &m = meta[i % META_SLOTS];
+            const bool masked = (m.cls & 0x100) != 0;
+            // two cells ahead: metadata; one cell ahead: S values -- neither depends on the product
+            fetch_meta(i + 2);
+            float n_lo[8], n_hi[8];
+            load_s(i + 1, n_lo, n_hi);
             const unsigned b = n_acc & 1u;
             ok = epilogue_all(wait_bar(&acc_full[b], (n_acc >> 1) & 1u));
             if (!ok) break;
@@ -334,7 +363,8 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(&acc_empty[b]);  // the accumulator may be overwritten: the next cell's MMAs run during the pick
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[b]);  // the accumulator may be overwritten: the next cell's MMAs run during the pick
                 float *crow = Ct + row * CT_STRIDE + cgroup * 16;
 #pragma unroll
                 for (int c = 0; c < 16; c += 4)
@@ -345,10 +375,12 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
             if (masked) {
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const unsigned lo = (unsigned)mk[u], hi = (unsigned)(mk[u] >> 32);
+                    const unsigned long long mk = m.mask[ew * 8 + u];
+                    const unsigned lo = (unsigned)mk, hi = (unsigned)(mk >> 32);
+                    const int32_t bs = m.base[ew * 8 + u];
                     const float *cr = Ct + (ew * 8 + u) * CT_STRIDE;
-                    if ((lo >> lane) & 1u) __stcs(P + bs[u] + __popc(lo & below), cr[lane] * s_lo[u]);
-                    if ((hi >> lane) & 1u) __stcs(P + bs[u] + __popc(lo) + __popc(hi & below), cr[lane + 32] * s_hi[u]);
+                    if ((lo >> lane) & 1u) __stcs(P + bs + __popc(lo & below), cr[lane] * s_lo[u]);
+                    if ((hi >> lane) & 1u) __stcs(P + bs + __popc(lo) + __popc(hi & below), cr[lane + 32] * s_hi[u]);
                 }
             } else {
                 // per-nonzero lists, eight nonzeros per thread and trip, the loads of a trip grouped by dependency
@@ -362,9 +394,9 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     float sv[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        const int i = i0 + et + u * N_EPILOGUE;
-                        code[u] = i < dc.count ? (unsigned)__ldcs(crc + i) : 0u;
-                        o[u] = i < dc.count ? __ldcs(cidx + i) : -1;
+                        const int j = i0 + et + u * N_EPILOGUE;
+                        code[u] = j < dc.count ? (unsigned)__ldcs(crc + j) : 0u;
+                        o[u] = j < dc.count ? __ldcs(cidx + j) : -1;
                     }
 #pragma unroll
                     for (int u = 0; u < 8; ++u) sv[u] = (sval && o[u] >= 0) ? __ldg(sval + o[u]) : 1.f;
@@ -373,11 +405,16 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                         if (o[u] >= 0) P[o[u]] = Ct[(code[u] >> 8) * CT_STRIDE + (code[u] & 255u)] * sv[u];
                 }
             }
-            // the next cell's masks and base indices, in flight across the barrier and the next wait
-            if (cell + gridDim.x < n_cells) fetch_meta(cell + gridDim.x);
-            epilogue_sync();  // before the next cell's block overwrites it
+            asm volatile("cp.async.wait_group 0;" ::: "memory");  // the metadata fetched at the top of this iteration
+            epilogue_sync();  // ... is visible to everybody; and the next cell's block may overwrite this one
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                s_lo[u] = n_lo[u];
+                s_hi[u] = n_hi[u];
+            }
             ++n_acc;
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     if (!ok && lane == 0) atomicExch(dev_status, (int)DEV_MBARRIER_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
