@@ -104,27 +104,40 @@ int gen_uniform(int64_t M, int64_t N, double density, uint64_t seed, sddmm_mtx_s
     const int64_t target = (int64_t)std::floor(density * cells);
     if (target < 0 || (double)target > cells || target >= INT32_MAX) return SDDMM_INVALID_ARG;
     const Rng r(seed, S_STRUCT);
-    std::vector<uint64_t> keys;
-    uint64_t drawn = 0;
     const uint64_t total = (uint64_t)M * (uint64_t)N;
-    while ((int64_t)keys.size() < target) {
-        const uint64_t want = (uint64_t)(target - (int64_t)keys.size());
+    // more than half of the cells: draw the cells that stay EMPTY instead (drawing without replacement by
+    // rejection slows down as the matrix fills up)
+    const bool complement = (uint64_t)target * 2 > total;
+    const int64_t want_cells = complement ? (int64_t)(total - (uint64_t)target) : target;
+    std::vector<uint64_t> keys;  // linear cell ids, sorted, distinct
+    uint64_t drawn = 0;
+    while ((int64_t)keys.size() < want_cells) {
+        const uint64_t want = (uint64_t)(want_cells - (int64_t)keys.size());
         const uint64_t batch = want + want / 16 + 16;
-        for (uint64_t i = 0; i < batch; ++i) {
-            const uint64_t cell = r.u64(drawn++) % total;
-            keys.push_back(((cell / (uint64_t)N) << 32) | (cell % (uint64_t)N));
-        }
+        for (uint64_t i = 0; i < batch; ++i) keys.push_back(r.u64(drawn++) % total);
         std::sort(keys.begin(), keys.end());
         keys.erase(std::unique(keys.begin(), keys.end()), keys.end());
     }
-    if ((int64_t)keys.size() > target) {
+    if ((int64_t)keys.size() > want_cells) {
+        // drop the surplus cells with the largest hash: keeps the choice uniform and seeded
         std::vector<std::pair<uint64_t, uint64_t>> h(keys.size());
         for (size_t i = 0; i < keys.size(); ++i) h[i] = {mix64(keys[i] ^ seed), keys[i]};
-        std::nth_element(h.begin(), h.begin() + target, h.end());
-        keys.resize((size_t)target);
-        for (int64_t i = 0; i < target; ++i) keys[(size_t)i] = h[(size_t)i].second;
+        std::nth_element(h.begin(), h.begin() + want_cells, h.end());
+        keys.resize((size_t)want_cells);
+        for (int64_t i = 0; i < want_cells; ++i) keys[(size_t)i] = h[(size_t)i].second;
         std::sort(keys.begin(), keys.end());
     }
+    if (complement) {
+        std::vector<uint64_t> kept;
+        kept.reserve((size_t)target);
+        size_t j = 0;
+        for (uint64_t c = 0; c < total; ++c) {
+            if (j < keys.size() && keys[j] == c) { ++j; continue; }
+            kept.push_back(c);
+        }
+        keys.swap(kept);
+    }
+    for (auto &c : keys) c = ((c / (uint64_t)N) << 32) | (c % (uint64_t)N);  // row-major cell id -> (row, col) key, order kept
     keys_to_coo(keys, m);
     return SDDMM_OK;
 }
