@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c5", "c5b"])
     ap.add_argument("--k", type=int, default=0, help="override K of the workload")
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (c3/c4), for quick runs")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "panel", "gather"])
@@ -81,6 +81,10 @@ def make_problem(args, device):
         s = args.scale or 22
         p = synth.rmat_c4(K=args.k or 256, device=device, scale=s)
         name = f"c4_rmat_scale{s}_ef24"
+    elif w == "c5b":
+        # the "2 % of rows and columns are global" reading of the same configuration: 1311 global rows / columns
+        p = synth.attention_mask(n_global=1311, K=args.k or 64, device=device)
+        name = "c5b_attention_65536_band256_g1311"
     else:
         p = synth.attention_mask(K=args.k or 64, device=device)
         name = "c5_attention_65536_band256_g80"
@@ -257,11 +261,11 @@ def run_reference(args, rank):
 
 
 def p_workload(args):
-    K = args.k or {"c1": 32, "c2": 256, "c3": 128, "c4": 256, "c5": 64}[args.workload]
+    K = args.k or {"c1": 32, "c2": 256, "c3": 128, "c4": 256, "c5": 64, "c5b": 64}[args.workload]
     s3, s4 = args.scale or 20, args.scale or 22
     return {"c1": "c1_uniform_4096x4096_d0.001", "c2": "c2_bagofwords_12419x1500_nnz746316",
             "c3": f"c3_rmat_scale{s3}_ef16", "c4": f"c4_rmat_scale{s4}_ef24",
-            "c5": "c5_attention_65536_band256_g80"}[args.workload] + f"_K{K}"
+            "c5": "c5_attention_65536_band256_g80", "c5b": "c5b_attention_65536_band256_g1311"}[args.workload] + f"_K{K}"
 
 
 def main():
