@@ -161,6 +161,10 @@ def hbm_peak():
 NCU_DRAM_BYTES_PER_LAUNCH = {
     ("c4_rmat_scale22_ef24_K256", "ring"): 47_011_806_208 + 391_284_992,   # profiles/sddmm_ring_kernel_c4_rmat_scale22_K256.md
     ("c4_rmat_scale22_ef24_K256", "panel"): 56_620_000_000 + 697_190_000,  # profiles/sddmm_panel_and_gather_kernels_rmat_K256.md
+    ("c4_rmat_scale22_ef24_K32", "ring"): 3_147_090_176 + 383_378_688,     # same file, section "other K"
+    ("c4_rmat_scale22_ef24_K128", "ring"): 18_132_192_512 + 389_742_080,
+    ("c4_rmat_scale22_ef24_K1024", "ring"): 271_263_138_048 + 392_786_176,
+    ("c3_rmat_scale20_ef16_K128", "ring"): 1_785_516_000 + 66_651_648,     # profiles/sddmm_ring_small_kernel_c3_rmat_scale20_K128.md
 }
 
 
