@@ -145,6 +145,36 @@ SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
  * uploads between them are not counted. */
 SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
 
+/* Which kernels the last sddmm_execute() on this plan launched: "ring", "ring_small",
+ * "panel", "gather", "dense_tc+ring_small", ... (static storage).  The reference has one
+ * kernel, comp_kernel_COO (HiPC18/src/kernel.h:2), and nothing to report. */
+SDDMM_API const char *sddmm_last_kernel_name(sddmm_plan_t p);
+
+/*
+ * Wait for everything enqueued on the handle's stream and report the device
+ * status word: SDDMM_DEVICE_TIMEOUT if a bounded device-side wait of any earlier
+ * call gave up -- the way to learn the outcome of SDDMM_FLAG_ASYNC calls.  The
+ * reference's equivalent is cudaEventSynchronize(stop) (HiPC18/src/sddmm.cu:110).
+ */
+SDDMM_API int sddmm_sync(sddmm_handle_t h);
+
+/*
+ * Self-check of a result on the device: every stride-th nonzero is recomputed in
+ * float64 and compared per nonzero with |P - ref| <= tol * max(|ref|, A),
+ * A = sum_t |w_t h_t| (|s|).  W, H, Sval (or NULL) and P as passed to
+ * sddmm_execute(): host or device arrays (host arrays are staged for the call).  Counterpart: the reference's in-line comparison of
+ * the GPU result with its CPU result (HiPC18_mpi/sddmm.cu:318-334; absolute 1e-4).
+ * Any of the three outputs may be NULL.
+ */
+SDDMM_API int sddmm_check_result(sddmm_plan_t p, const float *W, const float *H, const float *Sval,
+                                 const float *P, int64_t stride, double tol, double *max_scaled_err,
+                                 int64_t *n_checked, int64_t *n_bad);
+
+/* Host-only self-test (no GPU needed): the per-kernel cache of shared-memory
+ * opt-ins is keyed by device ordinal, so a second GPU in the same process makes
+ * its own opt-in.  No counterpart in the reference (one GPU, static shared memory). */
+SDDMM_API int sddmm_selftest_optin_cache(void);
+
 /*
  * The rows of W (which = 0) or of H (which = 1) that an SDDMM over this plan
  * reads: ascending ids of the rows / columns of S that hold at least one
@@ -234,7 +264,9 @@ SDDMM_API int sddmm_plan_count_cols(sddmm_plan_t p, int64_t *n_nonempty_cols);
  *              SDDMM_INVALID_ARG and a message in errbuf (use
  *              sddmm_plan_count_cols for larger matrices).
  *   cuda_stream : cudaStream_t to run on (NULL = the default stream); the call
- *              returns after the count has been copied back.
+ *              returns after the count has been copied back, i.e. it waits for
+ *              the stream, and is refused (SDDMM_INVALID_ARG) on a stream that
+ *              is being captured.
  * The first call on each device also looks up the scratch array's device address;
  * make that first call outside any stream capture.  All calls on a device share
  * the scratch, which keeps the previous call's contents: every call clears what

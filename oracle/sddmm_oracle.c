@@ -5,7 +5,7 @@
  *
  * Every function restates, in plain C, one function of the reference
  * (isratnisa/SDDMM_GPU); the reference location is cited above each one.
- * Parity is pinned: tests/test_oracle_vs_reference.py compares each function
+ * Parity is pinned: tests/test_oracle_golden.py compares each function
  * with the reference's own code compiled from its sources (oracle/ref_bridge.cu)
  * and with the fixtures under tests/golden/ that were produced by that code.
  *

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
+    "sddmm_last_kernel_name", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
     "sddmm_mtx_close", "sddmm_mtx_open_ex", "sddmm_coo_save_binary", "sddmm_coo_sort_rows_gpu", "sddmm_gen_open", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
 
@@ -78,6 +79,12 @@ def lib():
     L.sddmm_destroy_plan.argtypes = [vp]
     L.sddmm_execute.argtypes = [vp, vp, vp, vp, vp, u32]
     L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    L.sddmm_last_kernel_name.restype = C.c_char_p
+    L.sddmm_last_kernel_name.argtypes = [vp]
+    L.sddmm_sync.argtypes = [vp]
+    L.sddmm_check_result.argtypes = [vp, vp, vp, vp, vp, i64, C.c_double, C.POINTER(C.c_double), C.POINTER(i64),
+                                     C.POINTER(i64)]
+    L.sddmm_selftest_optin_cache.argtypes = []
     L.sddmm_last_transfer_bytes.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.sddmm_plan_used_lines.argtypes = [vp, C.c_int, C.POINTER(vp), C.POINTER(i64)]
     L.sddmm_upload_rows.argtypes = [vp, vp, vp, vp, i64, C.c_int, vp]
@@ -128,8 +135,24 @@ def _ptr(a):
     raise TypeError(f"cannot take the address of {type(a)}")
 
 
+CUDA_STREAM_LEGACY = 0x1  # cudaStreamLegacy: the handle that names the legacy default stream explicitly
+
+
+def _is_cuda_tensor(a):
+    return hasattr(a, "is_cuda") and a.is_cuda
+
+
 class Handle:
-    """One engine instance bound to one CUDA device (sddmm_create)."""
+    """One engine instance bound to one CUDA device (sddmm_create).
+
+    Stream ordering.  The engine launches on one CUDA stream.  Unless set_stream()
+    has been called, every call that is given a CUDA torch tensor first points the
+    engine at torch's CURRENT stream of the handle's device, so the call is ordered
+    after the work that produced its inputs and before whatever the caller
+    enqueues next on that stream -- no torch.cuda.synchronize() is needed around
+    it.  After an explicit set_stream() the caller owns the ordering: inputs must
+    be ready on that stream, and results are ready on it.  Calls with host arrays
+    only run on the handle's own stream and return when the result is complete."""
 
     def __init__(self, device=0):
         self._h = C.c_void_p()
@@ -138,6 +161,16 @@ class Handle:
             self._h = None
             raise SddmmError(st)
         self.device = device
+        self._explicit_stream = False
+
+    def _follow_torch_stream(self, *args):
+        """Launch on torch's current stream when a CUDA tensor is among the arguments
+        (and the caller has not chosen a stream)."""
+        if self._explicit_stream or not any(_is_cuda_tensor(a) for a in args):
+            return
+        import torch
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(lib().sddmm_set_stream(self._h, s if s else CUDA_STREAM_LEGACY))
 
     def close(self):
         if self._h:
@@ -164,6 +197,12 @@ class Handle:
     def set_stream(self, cuda_stream):
         """cuda_stream: integer cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream) or None."""
         self._check(lib().sddmm_set_stream(self._h, cuda_stream))
+        self._explicit_stream = cuda_stream is not None
+
+    def sync(self):
+        """Wait for the handle's stream; raises SddmmError(DEVICE_TIMEOUT) if a bounded device-side wait of
+        an earlier (possibly FLAG_ASYNC) call gave up."""
+        self._check(lib().sddmm_sync(self._h))
 
     def upload_rows(self, host, dev, d_row_ids, n_rows, K, cuda_stream=None):
         """Copy the listed rows of a pinned host array to the same rows of a device array (the GPU
@@ -174,6 +213,7 @@ class Handle:
     def coo_sort_rows(self, M, N, rows, cols, vals, transpose=False):
         """sddmm_coo_sort_rows on the GPU, in place (numpy arrays or device tensors); returns (M, N)."""
         m, n = C.c_int64(M), C.c_int64(N)
+        self._follow_torch_stream(rows, cols, vals)
         self._check(lib().sddmm_coo_sort_rows_gpu(self._h, C.byref(m), C.byref(n), rows.shape[0], _ptr(rows), _ptr(cols),
                                                   _ptr(vals), 1 if transpose else 0))
         return m.value, n.value
@@ -185,6 +225,7 @@ class Handle:
         if is_dev:
             flags |= PLAN_DEVICE_INDICES
         p = C.c_void_p()
+        self._follow_torch_stream(rows, cols)
         st = lib().sddmm_plan_coo(self._h, M, N, nnz, _ptr(rows), _ptr(cols), K, panel_rows_hint, col_tile_hint,
                                   flags, C.byref(p))
         self._check(st)
@@ -194,6 +235,7 @@ class Handle:
     def sddmm_coo(self, M, N, rows, cols, W, H, K, P, Sval=None, nnz=None):
         if nnz is None:
             nnz = int(rows.shape[0])
+        self._follow_torch_stream(rows, cols, W, H, P, Sval)
         self._check(lib().sddmm_coo(self._h, M, N, nnz, _ptr(rows), _ptr(cols), _ptr(Sval), _ptr(W), _ptr(H), K,
                                     _ptr(P)))
 
@@ -220,7 +262,20 @@ class Plan:
             pass
 
     def execute(self, W, H, P, Sval=None, flags=0):
+        self.handle._follow_torch_stream(W, H, P, Sval)
         self.handle._check(lib().sddmm_execute(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P), flags))
+
+    def last_kernel_name(self):
+        return lib().sddmm_last_kernel_name(self._p).decode()
+
+    def check_result(self, W, H, P, Sval=None, stride=1, tol=1e-4):
+        """float64 recomputation of every stride-th nonzero on the device (sddmm_check_result):
+        returns (max scaled error, nonzeros checked, nonzeros out of tolerance)."""
+        worst, n, bad = C.c_double(), C.c_int64(), C.c_int64()
+        self.handle._follow_torch_stream(W, H, P, Sval)
+        self.handle._check(lib().sddmm_check_result(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P), stride, tol,
+                                                    C.byref(worst), C.byref(n), C.byref(bad)))
+        return worst.value, n.value, bad.value
 
     def last_kernel_ms(self):
         ms = C.c_float()

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 #include <string>
 
 #include "sddmm_b200.h"
@@ -35,6 +36,37 @@ struct DenseCell {
     int32_t count;
     int32_t cls;
 };
+
+// The opt-in to more than 48 KB of dynamic shared memory (cudaFuncSetAttribute) is a
+// property of a kernel ON ONE DEVICE: a process that drives several GPUs must make it
+// on each of them.  One cache per kernel instantiation remembers the largest size
+// already granted, per device ordinal; devices beyond the table are never cached.
+struct SmemOptinCache {
+    static constexpr int MAX_DEVICES = 64;
+    std::atomic<size_t> granted[MAX_DEVICES];
+    SmemOptinCache() { for (auto &g : granted) g.store(0, std::memory_order_relaxed); }
+    bool needs(int device, size_t bytes) const
+    {
+        return device < 0 || device >= MAX_DEVICES || bytes > granted[device].load(std::memory_order_acquire);
+    }
+    void record(int device, size_t bytes)
+    {
+        if (device >= 0 && device < MAX_DEVICES) granted[device].store(bytes, std::memory_order_release);
+    }
+};
+
+// Makes the opt-in for `kern` on the current device unless `cache` says it holds.
+template <class Kern>
+inline cudaError_t optin_dynamic_smem(Kern kern, size_t bytes, SmemOptinCache &cache)
+{
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (!cache.needs(device, bytes)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) cache.record(device, bytes);
+    return e;
+}
 
 // Device status word written by kernels whose bounded waits give up.
 enum DeviceStatus : int { DEV_OK = 0, DEV_MBARRIER_TIMEOUT = 1 };
@@ -109,6 +141,16 @@ cudaError_t launch_dense_cells_tc(const DenseCell *cells, int64_t n_cells, const
 cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                               const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted,
                               int sm_count, unsigned long long *work_counter, cudaStream_t stream);
+
+// float64 recomputation of every stride-th nonzero on the device (see check.cu).
+struct CheckResult {
+    unsigned long long n_checked;
+    unsigned long long n_bad;      // sampled nonzeros with |P - ref| > tol * max(|ref|, A), or not finite
+    double max_scaled_err;         // max |P - ref| / max(|ref|, A)
+};
+cudaError_t launch_check_result(const int32_t *rows, const int32_t *cols, const float *sval, const float *W, const float *H,
+                                const float *P, int64_t nnz, int K, int64_t stride, double tol, CheckResult *d_out,
+                                int sm_count, cudaStream_t stream);
 
 // Self-test of the bounded-wait path: one warp waits (with a short poll limit) on
 // an mbarrier that nothing ever arrives on, gives up, records DEV_MBARRIER_TIMEOUT

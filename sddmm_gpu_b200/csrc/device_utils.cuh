@@ -12,8 +12,8 @@ namespace dev {
 
 constexpr unsigned FULL = 0xffffffffu;
 // Upper bound on polls of an mbarrier before a CTA gives up and reports
-// DEV_MBARRIER_TIMEOUT.  try_wait itself blocks for a hardware-defined slice, so
-// this is far beyond any legitimate copy latency but still finite.
+// DEV_MBARRIER_TIMEOUT: the backstop behind the wall-clock budget of
+// mbar_wait_bounded (MBAR_WAIT_BUDGET_NS), far beyond any legitimate copy latency.
 constexpr int MBAR_SPIN_LIMIT = 1 << 20;
 
 __device__ __forceinline__ float4 ld_h(const float4 *p)
@@ -90,14 +90,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity)
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Wall-clock budget of one bounded wait.  The poll count alone says little about
+// time (every try_wait may block for a hardware-defined slice before it answers),
+// so the loop also reads the nanosecond timer every 64 polls and gives up once the
+// budget is spent; the poll limit stays as a backstop should the timer stand still.
+constexpr unsigned long long MBAR_WAIT_BUDGET_NS = 2000000000ull;  // 2 s
+struct WaitClock {
+    unsigned long long start = 0;
+    __device__ __forceinline__ bool expired(int it, unsigned long long budget_ns = MBAR_WAIT_BUDGET_NS)
+    {
+        if ((it & 63) != 63) return false;
+        const unsigned long long now = globaltimer_ns();
+        if (start == 0) {
+            start = now;
+            return false;
+        }
+        return now - start > budget_ns;
+    }
+};
 // Bounded wait: false when the limit ran out.  Polls back off with a short
 // sleep so that a waiting warp does not take issue slots from working ones.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, unsigned parity)
 {
+    WaitClock clock;
 #pragma unroll 1
     for (int it = 0; it < MBAR_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(it < 16 ? 32 : 256);
+        if (clock.expired(it)) return false;
     }
     return false;
 }

@@ -92,6 +92,7 @@ struct sddmm_plan_s {
     int32_t *d_used_rows = nullptr, *d_used_cols = nullptr;  // ascending ids of the rows / columns holding a nonzero
     int64_t n_used_rows = 0, n_used_cols = 0;
     int64_t last_h2d_bytes = 0, last_d2h_bytes = 0;  // moved by the last sddmm_execute
+    const char *last_kernel = "none";                // kernels the last sddmm_execute launched
 };
 
 namespace {
@@ -604,7 +605,9 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         h->last_error = "W and H must be 16-byte aligned on the device";
         return SDDMM_INVALID_ARG;
     }
+    const char *ring_name = p->K <= 128 ? "ring_small" : "ring";
     if (pipelined) {
+        p->last_kernel = p->K <= 128 ? "ring_small (pipelined chunks)" : "ring (pipelined chunks)";
         CUDA_TRY(h, ensure_pipeline(h));
         const int32_t *cols_p = p->d_cols_hint ? p->d_cols_hint : p->d_cols;
         for (int i = 0; i < p->n_pipe; ++i) {
@@ -651,6 +654,17 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
     if (!forced && !tiled_out && p->dense.n_cells > 0) {
         // locally dense plan: dense cells as small dense products, the rest gathered
+        {
+            static const char *const names[3][3] = {
+                {"dense_fma", "dense_fma+ring", "dense_fma+panel"},
+                {"dense_mma_sync", "dense_mma_sync+ring", "dense_mma_sync+panel"},
+                {"dense_tc", "dense_tc+ring", "dense_tc+panel"}};
+            const int rest = p->dense.n_sparse == 0 ? 0 : (ring_supports(p->K) ? 1 : 2);
+            p->last_kernel = names[h->dense_mode][rest];
+            if (rest == 1 && p->K <= 128)
+                p->last_kernel = h->dense_mode == 2 ? "dense_tc+ring_small"
+                                                    : (h->dense_mode == 1 ? "dense_mma_sync+ring_small" : "dense_fma+ring_small");
+        }
         if (h->dense_mode == 2)
             CUDA_TRY(h, launch_dense_cells_tc(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
                                               p->dense.row_base, p->dense.dense_rows, p->dense.n_dense_rows,
@@ -670,6 +684,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
                                          p->dense.perm_s, dS, dW, dH, dP, p->K, p->cfg, h->sm_count, h->d_status, s));
         }
     } else if (use_gather) {
+        p->last_kernel = "gather";
         CUDA_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
     } else {
         const bool tiled = p->d_perm != nullptr;
@@ -684,6 +699,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             h->last_error = "SDDMM_FLAG_TILED_ORDER with S values is not supported on a multi-tile plan";
             return SDDMM_INVALID_ARG;
         }
+        p->last_kernel = use_ring ? ring_name : "panel";
         if (use_ring)
             CUDA_TRY(h, launch_ring(rows_p, p->d_cols_hint ? p->d_cols_hint : cols_p, perm, dS, dW, dH, dP, p->nnz, p->K,
                                     p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status, s));
@@ -811,6 +827,73 @@ int sddmm_last_transfer_bytes(sddmm_plan_t p, int64_t *h2d_bytes, int64_t *d2h_b
     if (!p) return SDDMM_INVALID_ARG;
     if (h2d_bytes) *h2d_bytes = p->last_h2d_bytes;
     if (d2h_bytes) *d2h_bytes = p->last_d2h_bytes;
+    return SDDMM_OK;
+}
+
+const char *sddmm_last_kernel_name(sddmm_plan_t p) { return p ? p->last_kernel : ""; }
+
+int sddmm_sync(sddmm_handle_t h)
+{
+    if (!h) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    return check_device_status(h);
+}
+
+int sddmm_check_result(sddmm_plan_t p, const float *W, const float *H, const float *Sval, const float *P,
+                       int64_t stride, double tol, double *max_scaled_err, int64_t *n_checked, int64_t *n_bad)
+{
+    if (!p || stride < 1 || !(tol > 0)) return SDDMM_INVALID_ARG;
+    sddmm_handle_s *h = p->h;
+    if (max_scaled_err) *max_scaled_err = 0.0;
+    if (n_checked) *n_checked = 0;
+    if (n_bad) *n_bad = 0;
+    if (p->nnz == 0) return SDDMM_OK;
+    if (!W || !H || !P) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    // host arrays are staged for this call only
+    struct Tmp {
+        void *p[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        ~Tmp() { for (void *q : p) if (q) cudaFree(q); }
+    } tmp;
+    auto stage = [&](int slot, const float *src, size_t count, const float **dst) -> cudaError_t {
+        if (!src || is_device_ptr(src)) { *dst = src; return cudaSuccess; }
+        cudaError_t e = cudaMalloc(&tmp.p[slot], sizeof(float) * (count ? count : 1));
+        if (e != cudaSuccess) return e;
+        *dst = (const float *)tmp.p[slot];
+        return cudaMemcpyAsync(tmp.p[slot], src, sizeof(float) * count, cudaMemcpyHostToDevice, h->stream);
+    };
+    const float *dW, *dH, *dS, *dP;
+    CUDA_TRY(h, stage(0, W, (size_t)p->M * p->K, &dW));
+    CUDA_TRY(h, stage(1, H, (size_t)p->N * p->K, &dH));
+    CUDA_TRY(h, stage(2, Sval, (size_t)p->nnz, &dS));
+    CUDA_TRY(h, stage(3, P, (size_t)p->nnz, &dP));
+    CheckResult host{};
+    CUDA_TRY(h, cudaMalloc(&tmp.p[4], sizeof(CheckResult)));
+    CheckResult *d_out = (CheckResult *)tmp.p[4];
+    cudaError_t e = launch_check_result(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, stride, tol, d_out, h->sm_count,
+                                        h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&host, d_out, sizeof(host), cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    if (e != cudaSuccess) return fail_cuda(h, e, "sddmm_check_result");
+    if (max_scaled_err) *max_scaled_err = host.max_scaled_err;
+    if (n_checked) *n_checked = (int64_t)host.n_checked;
+    if (n_bad) *n_bad = (int64_t)host.n_bad;
+    return SDDMM_OK;
+}
+
+int sddmm_selftest_optin_cache(void)
+{
+    // host-only: the shared-memory opt-in cache must be keyed by device ordinal
+    SmemOptinCache c;
+    if (!c.needs(0, 1024) || !c.needs(1, 1024)) return SDDMM_INVALID_ARG;
+    c.record(0, 4096);
+    if (c.needs(0, 4096) || c.needs(0, 1024)) return SDDMM_INVALID_ARG;   // device 0 holds it
+    if (!c.needs(1, 1024) || !c.needs(0, 8192)) return SDDMM_INVALID_ARG;  // device 1 does not; larger sizes do not either
+    if (!c.needs(-1, 1) || !c.needs(SmemOptinCache::MAX_DEVICES, 1)) return SDDMM_INVALID_ARG;
+    c.record(SmemOptinCache::MAX_DEVICES, 1);                               // out of table: never cached
+    if (!c.needs(SmemOptinCache::MAX_DEVICES, 1)) return SDDMM_INVALID_ARG;
     return SDDMM_OK;
 }
 

@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "sddmm_b200.h"
@@ -35,7 +36,9 @@ static_assert(SCRATCH_BYTES == SDDMM_NOALLOC_SCRATCH_BYTES, "header and source d
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SCRATCH_BYTES];
 
 constexpr int MAX_DEVICES = 64;
-unsigned char *g_scratch_addr[MAX_DEVICES];  // device address of the array, per device, once resolved
+// device address of the array, per device, once resolved (two threads making a device's first call
+// both resolve the same address; the atomic only makes the publication well defined)
+std::atomic<unsigned char *> g_scratch_addr[MAX_DEVICES];
 
 void fail(char *errbuf, int len, const char *msg, cudaError_t e = cudaSuccess)
 {
@@ -91,10 +94,26 @@ extern "C" int sddmm_count_cols_noalloc(int device, const int32_t *d_cols, int64
         (void)cudaGetLastError();
         return SDDMM_NO_DEVICE;
     }
+    cudaStream_t s = (cudaStream_t)cuda_stream;
+    {
+        // the call hands back a number, so it ends by waiting for the stream: a stream that
+        // is being captured cannot be waited for, and trying would break the capture
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        e = cudaStreamIsCapturing(s, &cap);
+        if (e != cudaSuccess) {
+            fail(errbuf, errbuf_len, "cudaStreamIsCapturing", e);
+            (void)cudaGetLastError();
+            return SDDMM_CUDA_ERROR;
+        }
+        if (cap != cudaStreamCaptureStatusNone) {
+            fail(errbuf, errbuf_len, "sddmm_count_cols_noalloc waits for its result and cannot run on a capturing stream");
+            return SDDMM_INVALID_ARG;
+        }
+    }
     // One-time set-up per device, with that device current: ask the runtime where
     // this device's copy of the array lives.  This is the part of the first call
     // that must not fall inside a stream capture.
-    if (!g_scratch_addr[device]) {
+    if (!g_scratch_addr[device].load(std::memory_order_acquire)) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || !p) {
@@ -102,12 +121,11 @@ extern "C" int sddmm_count_cols_noalloc(int device, const int32_t *d_cols, int64
             (void)cudaGetLastError();
             return SDDMM_CUDA_ERROR;
         }
-        g_scratch_addr[device] = (unsigned char *)p;
+        g_scratch_addr[device].store((unsigned char *)p, std::memory_order_release);
     }
-    unsigned char *scratch = g_scratch_addr[device];
+    unsigned char *scratch = g_scratch_addr[device].load(std::memory_order_acquire);
     unsigned long long *count = (unsigned long long *)scratch;
     unsigned char *marks = scratch + HEADER_BYTES;
-    cudaStream_t s = (cudaStream_t)cuda_stream;
 
     // the previous call's count and marks are still there: clear what this call uses
     e = cudaMemsetAsync(scratch, 0, HEADER_BYTES + (size_t)N, s);

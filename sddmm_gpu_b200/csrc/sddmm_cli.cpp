@@ -26,7 +26,16 @@
 //   --gather           use the planless gather kernel
 //   --device D         CUDA device (default 0)
 //   --dump-p FILE      write P (float32, input nonzero order) to FILE
-//   --json FILE        write a small JSON report (ms, GFLOP/s, plan sizes)
+//   --json FILE        write a small JSON report: ms, GFLOP/s, the kernels that ran, plan sizes,
+//                      GPU count, host cores and the roofline figures (algorithmic bytes of the
+//                      call, achieved GB/s, and its fraction of --hbm-gbs when that is given)
+//   --hbm-gbs X        HBM bandwidth to report the roofline fraction against (GB/s)
+//   --check            recompute every nonzero in float64 on the GPU and compare per nonzero
+//                      (|P - ref| <= 1e-4 max(|ref|, sum_t |w_t h_t| |s|)): the in-line check the
+//                      reference's MPI program makes against its CPU result
+//                      (HiPC18_mpi/sddmm.cu:318-334); a failed check exits non-zero
+//   --seed S           W and H uniform in [0, 1) from a counter-based generator seeded with S
+//                      instead of the reference's srand48(0) initialisation
 //   --write-mtx FILE   write the input matrix as Matrix Market (e.g. to hand a
 //                      generated matrix to another program)
 //   --save-bin FILE    write the input matrix in the library's binary form, which
@@ -38,6 +47,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "sddmm_b200.h"
@@ -57,13 +67,25 @@ void initial(std::vector<float> &X, long n, int k)
     for (long i = 0; i < n * (long)k; ++i) X[(size_t)i] = (float)(0.1 * drand48());
 }
 
+// uniform [0, 1) from splitmix64(seed, stream, index): exact in fp32, the same on every host
+void seeded(std::vector<float> &X, uint64_t seed, uint64_t stream)
+{
+    for (size_t i = 0; i < X.size(); ++i) {
+        uint64_t z = seed * 0x9e3779b97f4a7c15ull + stream * 0xbf58476d1ce4e5b9ull + (uint64_t)i + 0x94d049bb133111ebull;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        z ^= z >> 31;
+        X[i] = (float)(uint32_t)(z >> 40) * (1.0f / 16777216.0f);
+    }
+}
+
 }  // namespace
 
 int main(int argc, char **argv)
 {
     if (argc < 5) {
         std::fprintf(stderr, "usage: %s input.mtx K tile_size_X tile_size_Y [--iters N] [--warmup N] "
-                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE] [--save-bin FILE] [--sort] [--expand-symmetric]\n"
+                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE] [--save-bin FILE] [--sort] [--expand-symmetric] [--check] [--seed S] [--hbm-gbs X]\n"
                              "       input may be gen:c1..c5 | gen:uniform:M:N:density | gen:zipf:M:N:nnz | "
                              "gen:rmat:scale:edge_factor | gen:band:M:half_width:g [:seed=S]\n", argv[0]);
         return 2;
@@ -75,7 +97,9 @@ int main(int argc, char **argv)
     int iters = 1, warmup = 0, device = 0;
     bool scale = true, gather = false;
     const char *dump_p = nullptr, *json = nullptr, *write_mtx = nullptr, *save_bin = nullptr;
-    bool sort_input = false;
+    bool sort_input = false, check = false, have_seed = false;
+    unsigned long long seed = 0;
+    double hbm_gbs = 0.0;
     uint32_t open_flags = 0;
     for (int i = 5; i < argc; ++i) {
         std::string a = argv[i];
@@ -97,6 +121,12 @@ int main(int argc, char **argv)
         else if (a == "--write-mtx") write_mtx = need("--write-mtx");
         else if (a == "--save-bin") save_bin = need("--save-bin");
         else if (a == "--sort") sort_input = true;
+        else if (a == "--check") check = true;
+        else if (a == "--hbm-gbs") hbm_gbs = std::atof(need("--hbm-gbs"));
+        else if (a == "--seed") {
+            seed = std::strtoull(need("--seed"), nullptr, 10);
+            have_seed = true;
+        }
         else if (a == "--expand-symmetric") open_flags |= SDDMM_MTX_EXPAND_SYMMETRIC;
         else {
             std::fprintf(stderr, "sddmm: unknown option %s\n", a.c_str());
@@ -117,7 +147,7 @@ int main(int argc, char **argv)
     std::vector<float> vals((size_t)nnz);
     st = sddmm_mtx_read(f, rows.data(), cols.data(), vals.data());
     if (st != SDDMM_OK) return die("reading input", st, "");
-    std::printf("\nTilesize: X = %d, tilesize: Y = %d, TB: %d\n", col_tile, panel_rows, 256);
+    std::printf("\nTilesize: X = %d, tilesize: Y = %d, TB: %d\n", col_tile, panel_rows, 512);  // BLOCKSIZE of the reference (util.h:19)
     sddmm_handle_t h = nullptr;
     st = sddmm_create(&h, device);
     if (st != SDDMM_OK) return die("creating the engine", st, "");
@@ -143,7 +173,10 @@ int main(int argc, char **argv)
     }
 
     std::vector<float> W((size_t)M * K), H((size_t)N * K), P((size_t)nnz);
-    if (K > 0) {
+    if (K > 0 && have_seed) {
+        seeded(W, seed, 1);
+        seeded(H, seed, 2);
+    } else if (K > 0) {
         initial(W, M, K);
         initial(H, N, K);
     }
@@ -175,6 +208,23 @@ int main(int argc, char **argv)
 
     sddmm_plan_info info;
     sddmm_plan_get_info(plan, &info);
+    const std::string kernel_name = sddmm_last_kernel_name(plan);
+    double check_err = -1.0;
+    long long check_n = 0, check_bad = 0;
+    if (check && nnz > 0) {
+        int64_t n_checked = 0, n_bad = 0;
+        st = sddmm_check_result(plan, W.data(), H.data(), sval, P.data(), 1, 1e-4, &check_err, &n_checked, &n_bad);
+        if (st != SDDMM_OK) {
+            int rc = die("checking", st, sddmm_last_error(h));
+            sddmm_destroy_plan(plan);
+            sddmm_destroy(h);
+            return rc;
+        }
+        check_n = n_checked;
+        check_bad = n_bad;
+        std::fprintf(stderr, "sddmm: check: %lld nonzeros recomputed in float64, %lld out of tolerance, max scaled error %.3g\n",
+                     check_n, check_bad, check_err);
+    }
     if (dump_p) {
         FILE *o = std::fopen(dump_p, "wb");
         if (!o || std::fwrite(P.data(), sizeof(float), (size_t)nnz, o) != (size_t)nnz) return die("writing P", SDDMM_IO_ERROR, dump_p);
@@ -184,17 +234,33 @@ int main(int argc, char **argv)
         FILE *o = std::fopen(json, "w");
         if (!o) return die("writing report", SDDMM_IO_ERROR, json);
         const double gflops = ms > 0 ? 2.0 * (double)nnz * K / (ms * 1e6) : 0.0;
+        // algorithmic bytes of one call: every touched row of W and H once, per nonzero a column index, an S
+        // value and a P store, plus the row pointer
+        int64_t n_cols_used = 0;
+        sddmm_plan_count_cols(plan, &n_cols_used);
+        const double alg_bytes = 4.0 * K * (double)(info.n_nonempty_rows + n_cols_used) + 12.0 * (double)nnz + 4.0 * (double)(M + 1);
+        const double achieved = ms > 0 ? alg_bytes / (ms * 1e6) : 0.0;
+        std::fprintf(o, "{\"roofline\": {\"bound\": \"hbm\", \"algorithmic_bytes\": %.0f, \"achieved_gbs\": %.3f, \"peak_gbs\": %s, "
+                        "\"frac\": %s}, \"gpus\": 1, \"host_cores\": %u, \"check\": {\"ran\": %s, \"n\": %lld, \"bad\": %lld, "
+                        "\"max_scaled_err\": %.6g}, ",
+                     alg_bytes, achieved, hbm_gbs > 0 ? std::to_string(hbm_gbs).c_str() : "null",
+                     hbm_gbs > 0 ? std::to_string(achieved / hbm_gbs).c_str() : "null", std::thread::hardware_concurrency(),
+                     check ? "true" : "false", check_n, check_bad, check_err);
         std::fprintf(o,
-                     "{\"rows\": %lld, \"cols\": %lld, \"nnz\": %lld, \"K\": %d, \"kernel_ms\": %.6f, "
+                     "\"rows\": %lld, \"cols\": %lld, \"nnz\": %lld, \"K\": %d, \"kernel_ms\": %.6f, "
                      "\"gflops\": %.3f, \"plan_ms\": %.4f, \"panel_rows\": %d, \"col_tile\": %d, "
                      "\"n_col_tiles\": %d, \"work_items\": %lld, \"nonempty_rows\": %lld, \"scale_by_s\": %s, "
                      "\"kernel\": \"%s\"}\n",
                      (long long)M, (long long)N, (long long)nnz, K, ms, gflops, info.plan_ms, info.panel_rows,
                      info.col_tile, info.n_col_tiles, (long long)info.n_work_items, (long long)info.n_nonempty_rows,
-                     scale ? "true" : "false", gather ? "gather" : "panel");
+                     scale ? "true" : "false", kernel_name.c_str());
         std::fclose(o);
     }
     sddmm_destroy_plan(plan);
     sddmm_destroy(h);
+    if (check && check_bad > 0) {
+        std::fprintf(stderr, "sddmm: check failed\n");
+        return 3;
+    }
     return 0;
 }

@@ -221,13 +221,11 @@ cudaError_t launch_dense_cells(const DenseCell *cells, int64_t n_cells, const in
 {
     if (n_cells == 0) return cudaSuccess;
     const size_t smem = sizeof(float) * SMEM_FLOATS;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(sddmm_dense_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(sddmm_dense_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptinCache optin_fma, optin_tensor;  // per device
+    {
+        cudaError_t e = optin_dynamic_smem(sddmm_dense_kernel<false>, smem, optin_fma);
+        if (e == cudaSuccess) e = optin_dynamic_smem(sddmm_dense_kernel<true>, smem, optin_tensor);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     int64_t blocks = (int64_t)sm_count * 3;
     if (blocks > n_cells) blocks = n_cells;

@@ -432,11 +432,10 @@ cudaError_t launch_dense_cells_tc(const DenseCell *cells, int64_t n_cells, const
                                   int *dev_status, cudaStream_t stream)
 {
     if (n_cells == 0) return cudaSuccess;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(sddmm_dense_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    static SmemOptinCache optin;  // per device
+    {
+        cudaError_t e = optin_dynamic_smem(sddmm_dense_tc_kernel, TC_SMEM_BYTES, optin);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     int64_t blocks = sm_count;  // one persistent CTA per SM
     if (blocks > n_cells) blocks = n_cells;

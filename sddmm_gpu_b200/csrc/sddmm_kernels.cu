@@ -252,9 +252,11 @@ struct PanelSmem {
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, unsigned parity, volatile int *abort_flag)
 {
+    WaitClock clock;
     for (int it = 0; it < MBAR_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255) == 255 && *abort_flag) return false;
+        if (clock.expired(it)) return false;
     }
     return false;
 }
@@ -380,11 +382,10 @@ cudaError_t launch_panel_t(const WorkItem *items, int64_t n_items, const int32_t
                            int sm_count, int *dev_status, cudaStream_t stream)
 {
     auto kern = sddmm_panel_kernel<L, C, B, PANEL_WARPS>;
-    static size_t configured_smem = 0;  // largest opt-in made so far for this instantiation
-    if (cfg.smem_bytes > configured_smem) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);
+    static SmemOptinCache optin;  // largest opt-in made so far for this instantiation, per device
+    {
+        cudaError_t e = optin_dynamic_smem(kern, cfg.smem_bytes, optin);
         if (e != cudaSuccess) return e;
-        configured_smem = cfg.smem_bytes;
     }
     int64_t blocks = (int64_t)sm_count * cfg.ctas_per_sm;
     if (blocks > n_items) blocks = n_items;

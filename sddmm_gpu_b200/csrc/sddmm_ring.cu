@@ -281,13 +281,10 @@ cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32
     using R = RingShape<C>;
     const size_t smem = (size_t)RING_WARPS * RING_NG * R::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
     auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL, HAS_HINT>;
-    static bool configured = false;  // one opt-in per instantiation and process
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
+    static SmemOptinCache optin;  // one opt-in per instantiation and device
+    cudaError_t e = optin_dynamic_smem(kern, smem, optin);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
     if (e != cudaSuccess) return e;
     // blocks of groups handed out dynamically: about four blocks per warp on small
     // inputs, never fewer than 16 groups (the ring drains between blocks) or more than 128

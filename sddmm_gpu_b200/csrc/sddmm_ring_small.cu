@@ -195,13 +195,10 @@ cudaError_t launch_small_tt(const int32_t *rows, const int32_t *cols, const int3
     using R = SmallShape<RB>;
     const size_t smem = (size_t)SR_WARPS * SR_NG * R::SLOT_BYTES;
     auto kern = sddmm_ring_small_kernel<RB, HAS_PERM, HAS_SVAL, HAS_HINT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
+    static SmemOptinCache optin;  // one opt-in per instantiation and device
+    cudaError_t e = optin_dynamic_smem(kern, smem, optin);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
     if (e != cudaSuccess) return e;
     const int64_t n_groups = nnz / R::B;
     int64_t bg = n_groups / ((int64_t)sm_count * SR_WARPS * 4);

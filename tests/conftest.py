@@ -36,3 +36,16 @@ def engine():
     h = api.Handle(0)
     yield h
     h.close()
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How the checked nonzeros split by conditioning (see tests/helpers.py)."""
+    try:
+        from helpers import parity_stats as st
+    except Exception:
+        return
+    if st["checked"]:
+        terminalreporter.write_line(
+            f"parity: {st['checked']} nonzeros checked against the oracle; {st['well_conditioned']} well-conditioned "
+            f"(plain 1e-4 relative asserted), {st['between_1e-3_and_1e-2']} with 1e-3 A <= |ref| < 1e-2 A and "
+            f"{st['below_1e-3']} below 1e-3 A (magnitude-scaled bound only)")

@@ -180,6 +180,45 @@ def test_device_pointers_and_stream(engine):
     plan.close()
 
 
+def test_calls_follow_torch_current_stream_without_manual_sync():
+    """No torch.cuda.synchronize() around the calls: a handle that was not given a stream launches on
+    torch's current stream, so it sees operands that are still being produced on that stream and the
+    next torch operation on it sees the finished P."""
+    h = api.Handle(0)
+    try:
+        p = synth.uniform_sparse(M=4096, N=4096, density=0.01, K=256, device="cuda")
+        rows, cols = p["rows"], p["cols"]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            plan = h.plan_coo(p["M"], p["N"], rows, cols, p["K"])
+            big = torch.randn(8192, 8192, device="cuda")
+            for _ in range(4):
+                big = big @ big * 1e-4                       # keeps the stream busy for a while
+            W = torch.zeros_like(p["W"])
+            W += p["W"] + big[0, 0] * 0                      # W is complete only after the matrix products
+            P = torch.empty(rows.shape[0], device="cuda")
+            plan.execute(W, p["H"], P, p["vals"], api.FLAG_ASYNC)
+            total = P.double().sum()                         # enqueued right behind the kernel, same stream
+            W.zero_()                                        # and the operand is overwritten straight after
+            h.sync()                                         # waits for the stream and reads the device status word
+            got_total = float(total)
+        q = synth.to_numpy(p)
+        ref = oracle.cpu.sddmm_coo(q["rows"], q["cols"], q["W"], q["H"], q["vals"])
+        assert_parity(P.cpu().numpy(), q["rows"], q["cols"], q["W"], q["H"], q["vals"])
+        assert abs(got_total - float(ref.astype(np.float64).sum())) <= 1e-3 * float(np.abs(ref).sum())
+        assert plan.last_kernel_name() == "ring"
+        # the device-side float64 self-check agrees, and notices a damaged result
+        worst, n, bad = plan.check_result(p["W"], p["H"], P, p["vals"])
+        assert n == rows.shape[0] and bad == 0 and worst <= 1e-4
+        P[7] += 1.0
+        worst, n, bad = plan.check_result(p["W"], p["H"], P, p["vals"], stride=1)
+        assert bad == 1 and worst > 1e-4
+        plan.close()
+    finally:
+        h.close()
+
+
 def _scaled(problem_fn, **kw):
     return synth.to_numpy(problem_fn(device="cpu", **kw))
 
@@ -302,12 +341,20 @@ def test_cli_prints_reference_lines_and_matches_oracle(tmp_path):
     api.mtx_write(mtx, M, N, rows, cols, vals)
     out = str(tmp_path / "p.bin")
     for extra, sv in (([], vals), (["--no-scale-by-s"], None)):
-        res = subprocess.run([exe, mtx, str(K), "192", "50000", "--dump-p", out, "--json", str(tmp_path / "r.json")] + extra,
-                             capture_output=True, text=True)
+        res = subprocess.run([exe, mtx, str(K), "192", "50000", "--dump-p", out, "--json", str(tmp_path / "r.json"),
+                              "--check", "--hbm-gbs", "6500"] + extra, capture_output=True, text=True)
         assert res.returncode == 0, res.stderr
+        import json
+        rep = json.load(open(tmp_path / "r.json"))
+        assert rep["kernel"] == "panel" and rep["gpus"] == 1 and rep["host_cores"] >= 1   # 3000 nonzeros: the panel kernel
+        assert rep["check"]["ran"] and rep["check"]["n"] == rows.shape[0] and rep["check"]["bad"] == 0
+        assert rep["check"]["max_scaled_err"] <= 1e-4
+        n_cols_used = np.unique(cols).size
+        assert rep["roofline"]["algorithmic_bytes"] == 4 * K * (np.unique(rows).size + n_cols_used) + 12 * rows.shape[0] + 4 * (M + 1)
+        assert abs(rep["roofline"]["frac"] - rep["roofline"]["achieved_gbs"] / 6500) < 1e-6
         lines = [l for l in res.stdout.splitlines() if l.strip()]
         assert lines[0] == f"Matrix info:  rows: {M}, cols: {N}, nnz: {rows.shape[0]}"
-        assert lines[1].startswith("Tilesize: X = 50000, tilesize: Y = 192, TB: ")
+        assert lines[1] == "Tilesize: X = 50000, tilesize: Y = 192, TB: 512"   # the reference's line, verbatim (sddmm.cu:282)
         assert lines[2].startswith(f"Time for SDDMM with K = {K} : ") and lines[2].endswith(" ms")
         W = oracle.cpu.initial(M, K)     # the reference's operand initialisation
         H = oracle.cpu.initial(N, K)

@@ -301,3 +301,8 @@ def test_c_client_of_the_abi(tmp_path):
     run = subprocess.run([exe], capture_output=True, text=True)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "FAILED" not in run.stdout
+
+
+def test_shared_memory_optin_cache_is_per_device():
+    """A second GPU in the same process must make its own opt-in to large dynamic shared memory."""
+    assert api.lib().sddmm_selftest_optin_cache() == api.OK

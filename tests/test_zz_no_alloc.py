@@ -57,6 +57,16 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         handle.close()
 
 
+def test_indices_outside_the_matrix_are_ignored():
+    """-1 and N are not columns of the matrix: neither is counted and neither is written."""
+    N = 1000
+    cols = torch.tensor([-1, 0, 5, 5, N - 1, N, N + 7, -2 ** 31], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert api.count_cols_noalloc(cols, N) == 3
+    # the mark just behind the matrix stayed clear: a matrix one column wider sees column N once
+    assert api.count_cols_noalloc(cols, N + 1) == 4
+
+
 def test_sizes_beyond_the_builtin_scratch_are_rejected():
     cols = torch.zeros(4, dtype=torch.int32, device="cuda")
     with pytest.raises(api.SddmmError) as e:
