@@ -60,6 +60,7 @@ def parse_args():
     ap.add_argument("--col-tile", type=int, default=0, help="column-tile width passed to the plan (argv[4] of the CLI)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
 
@@ -156,21 +157,17 @@ def hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (keyed by workload and kernel; full-size captures, 1-pass metrics)
-NCU_DRAM_BYTES_PER_LAUNCH = {
-    ("c4_rmat_scale22_ef24_K256", "ring"): 47_011_806_208 + 391_284_992,   # profiles/sddmm_ring_kernel_c4_rmat_scale22_K256.md
-    ("c4_rmat_scale22_ef24_K256", "panel"): 56_620_000_000 + 697_190_000,  # profiles/sddmm_panel_and_gather_kernels_rmat_K256.md
-    ("c4_rmat_scale22_ef24_K32", "ring"): 3_147_090_176 + 383_378_688,     # same file, section "other K"
-    ("c4_rmat_scale22_ef24_K128", "ring"): 18_132_192_512 + 389_742_080,
-    ("c4_rmat_scale22_ef24_K1024", "ring"): 271_263_138_048 + 392_786_176,
-    ("c3_rmat_scale20_ef16_K128", "ring"): 1_785_516_000 + 66_651_648,     # profiles/sddmm_ring_small_kernel_c3_rmat_scale20_K128.md
-}
-
-
 def ncu_traffic(workload, kernel):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
-    return NCU_DRAM_BYTES_PER_LAUNCH.get((workload, kernel))
+    """The committed ncu DRAM-traffic record of the dominant kernel for this workload, if any
+    (profiles/dram_bytes.json: bytes per launch, the duration ncu saw, how it was captured)."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "profiles", "dram_bytes.json")))["captures"]
+    except Exception:
+        return None
+    for rec in table:
+        if rec["workload"] == workload and rec["kernel"] == kernel:
+            return rec
+    return None
 
 
 def sample_blocks(nnz, n_sample, n_blocks=64):
@@ -190,6 +187,101 @@ def build_cpu_sample(rows_h, cols_h, vals_h, W_of_rows, nnz, n_sample):
     uniq, inv = np.unique(r, return_inverse=True)
     Ws = W_of_rows(uniq)
     return inv.astype(np.int32), np.ascontiguousarray(c), np.ascontiguousarray(v), Ws, idx.shape[0]
+
+
+def oracle_sample_check(rows_d, cols_d, vals_d, W_d, H_d, results, n_sample=262_144, n_blocks=256):
+    """Worst scaled error |P - ref| / max(|ref|, A) of the given result arrays (device or host
+    tensors, aligned with rows_d) against the CPU oracle (sequential fp32, as the reference; A from its
+    float64 companion) on n_sample nonzeros taken as evenly spaced blocks over the WHOLE slice.  Only
+    the W and H rows the sample touches leave the device."""
+    import oracle
+    nnz = int(rows_d.shape[0])
+    if nnz == 0:
+        return 0.0, 0
+    idx = torch.from_numpy(sample_blocks(nnz, min(nnz, n_sample), n_blocks)).to(rows_d.device)
+    r, c = rows_d[idx].long(), cols_d[idx].long()
+    ur, ri = torch.unique(r, return_inverse=True)
+    uc, ci = torch.unique(c, return_inverse=True)
+    Ws, Hs = W_d[ur].cpu().numpy(), H_d[uc].cpu().numpy()
+    v = vals_d[idx].cpu().numpy()
+    rs, cs = ri.cpu().numpy().astype(np.int32), ci.cpu().numpy().astype(np.int32)
+    ref = oracle.cpu.sddmm_coo(rs, cs, Ws, Hs, v).astype(np.float64)
+    _, A = oracle.cpu.sddmm_coo_f64(rs, cs, Ws, Hs, v)
+    denom = np.maximum(np.maximum(np.abs(ref), A), 1e-30)
+    worst = 0.0
+    idx_h = idx.cpu()
+    for res in results:
+        got = (res[idx] if res.is_cuda else res[idx_h]).cpu().numpy().astype(np.float64)
+        err = np.abs(got - ref) / denom
+        worst = max(worst, float(np.max(np.where(np.isfinite(err), err, np.inf))))
+    return worst, int(idx.shape[0])
+
+
+def quick_run(handle, p, peak, steps=5, warmup=3):
+    """A short device-resident timing of one configuration: plan, warm-up, `steps` timed executes
+    (CUDA events on the launching stream), a sampled oracle check."""
+    from sddmm_gpu_b200 import api, synth
+    nnz = int(p["rows"].shape[0])
+    plan = handle.plan_coo(p["M"], p["N"], p["rows"], p["cols"], p["K"], p.get("panel_rows", 0), p.get("col_tile", 0))
+    info = plan.info()
+    P = torch.empty(nnz, device=p["rows"].device, dtype=torch.float32)
+    for _ in range(warmup):
+        plan.execute(p["W"], p["H"], P, p["vals"], api.FLAG_ASYNC)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        plan.execute(p["W"], p["H"], P, p["vals"], api.FLAG_ASYNC)
+        evs[i + 1].record()
+    handle.sync()
+    ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    mean_ms = sum(ms) / len(ms)
+    alg = synth.algorithmic_bytes(p["M"], nnz, p["K"], info.n_nonempty_rows, plan.count_cols())
+    worst, n_checked = oracle_sample_check(p["rows"], p["cols"], p["vals"], p["W"], p["H"], [P], 65_536, 64)
+    out = {"workload": p["workload"], "nnz": nnz, "K": p["K"], "ms_per_step": mean_ms, "ms_min": min(ms),
+           "gflops": 2.0 * nnz * p["K"] / (mean_ms * 1e-3) / 1e9, "algorithmic_bytes": alg,
+           "frac": alg / (mean_ms * 1e-3) / 1e9 / peak, "kernel": plan.last_kernel_name(),
+           "dense_cell_share": (info.n_dense_nnz / nnz) if nnz else 0.0, "plan_ms": info.plan_ms,
+           "parity_max_scaled_err": worst, "parity_n_checked": n_checked, "steps": steps}
+    plan.close()
+    return out
+
+
+def run_also(handle, device, peak, c4_pattern, args):
+    """The other benchmark configurations and the ends of config 4's K sweep, a few steps each, so that
+    one default run shows every configuration's time and roofline fraction (frac = algorithmic bytes /
+    time / measured HBM peak; recomputable from the entry)."""
+    from sddmm_gpu_b200 import synth
+    out = []
+
+    def go(make):
+        p = make()
+        try:
+            out.append(quick_run(handle, p, peak))
+        except Exception as ex:  # a failure here must not lose the headline line
+            out.append({"workload": p.get("workload", "?"), "error": str(ex)[:200]})
+        del p
+        torch.cuda.empty_cache()
+
+    def named(p, name):
+        p["workload"] = f"{name}_K{p['K']}"
+        return p
+
+    if c4_pattern is not None:
+        rows, cols, vals, M, N = c4_pattern
+        for K in (32, 1024):
+            def make(K=K):
+                g = torch.Generator(device=device)
+                g.manual_seed(synth.SEEDS["c4"] + K)
+                return dict(M=M, N=N, K=K, rows=rows, cols=cols, vals=vals, workload=f"c4_rmat_scale22_ef24_K{K}",
+                            W=torch.randn((M, K), generator=g, device=device) * 0.1,
+                            H=torch.randn((N, K), generator=g, device=device) * 0.1, panel_rows=192, col_tile=1 << 30)
+            go(make)
+    go(lambda: named(synth.uniform_sparse(device=device), "c1_uniform_4096x4096_d0.001"))
+    go(lambda: named(synth.bag_of_words(device=device), "c2_bagofwords_12419x1500_nnz746316"))
+    go(lambda: named(synth.rmat(device=device), "c3_rmat_scale20_ef16"))
+    go(lambda: named(synth.attention_mask(device=device), "c5_attention_65536_band256_g80"))
+    go(lambda: named(synth.attention_mask(n_global=1311, device=device), "c5b_attention_65536_band256_g1311"))
+    return out
 
 
 def cpu_port_rate(r, c, W, H, K, seconds):
@@ -217,15 +309,12 @@ def run_reference(args, rank):
     rows_h, cols_h, vals_h = (p[k].cpu().numpy() for k in ("rows", "cols", "vals"))
     H_h = p["H"].cpu().numpy()
     Wt = p["W"]
-    # sample sized from a quick probe with the port so that one step is a few seconds
+    # The sample depends on the workload only (never on a timing probe or on OMP_NUM_THREADS), so that every
+    # launch of this arm -- alone or as rank 0 under torchrun, on any box -- times the same nonzeros:
+    # all of them up to 60 GFLOP per step, else that many in 64 evenly spaced blocks.
+    n_step = int(min(nnz, max(200_000, 60e9 / (2.0 * K))))
     r, c, v, Ws, _ = build_cpu_sample(rows_h, cols_h, vals_h,
-                                      lambda u: Wt[torch.from_numpy(u).to(Wt.device)].cpu().numpy(), nnz, 2_000_000)
-    _, t = oracle.cpu.sddmm_coo(r[:200_000], c[:200_000], Ws, H_h, return_seconds=True)
-    _, t = oracle.cpu.sddmm_coo(r[:200_000], c[:200_000], Ws, H_h, return_seconds=True)
-    n_step = int(min(nnz, max(200_000, 200_000 * 3.0 / max(t, 1e-6))))
-    if n_step > r.shape[0]:
-        r, c, v, Ws, _ = build_cpu_sample(rows_h, cols_h, vals_h,
-                                          lambda u: Wt[torch.from_numpy(u).to(Wt.device)].cpu().numpy(), nnz, n_step)
+                                      lambda u: Wt[torch.from_numpy(u).to(Wt.device)].cpu().numpy(), nnz, n_step)
     n_step = min(n_step, r.shape[0])
     r, c, v = r[:n_step], c[:n_step], v[:n_step]
     del p
@@ -243,9 +332,9 @@ def run_reference(args, rank):
                 f"compacted, H whole; sddmm_CPU_COO by-value argument copies ({copy_s:.2f} s per call) subtracted, "
                 f"as its own timer excludes them")
     else:
-        kind, cores = "port", oracle.cpu.max_threads()
+        kind, cores = "port", os.cpu_count() or 1   # all host cores, whatever OMP_NUM_THREADS the launcher set
         for i in range(args.warmup + args.steps):
-            _, t = oracle.cpu.sddmm_coo(r, c, Ws, H_h, return_seconds=True)
+            _, t = oracle.cpu.sddmm_coo(r, c, Ws, H_h, return_seconds=True, threads=cores)
             if i >= args.warmup:
                 times.append(t)
         note = f"{n_step} nonzeros in 64 evenly spaced blocks ({100.0 * n_step / nnz:.2f}% of nnz), W rows compacted, H whole"
@@ -301,8 +390,6 @@ def main():
     handle.set_stream(stream.cuda_stream)
     kflag = {"auto": 0, "ring": api.FLAG_KERNEL_RING, "panel": api.FLAG_KERNEL_PANEL,
              "gather": api.FLAG_KERNEL_GATHER}[args.kernel]
-    kernel_name = args.kernel if args.kernel != "auto" else (
-        "ring" if K in (32, 64, 128, 256, 512, 1024) and nnz >= 65536 else "panel")
 
     # ---- sharding (identity at one GPU) --------------------------------------
     rows_host = rows.cpu().numpy()
@@ -337,6 +424,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    launches_before = handle.kernel_launches()
     # ---- device-resident timing ------------------------------------------------
     for _ in range(max(args.warmup, 3)):
         plan.execute(l_W, H, P, l_vals, kflag | api.FLAG_ASYNC)
@@ -361,20 +449,26 @@ def main():
     ms_per_step = total_ms_max / args.steps
     value = 2.0 * nnz * K / (ms_per_step * 1e-3) / 1e9
 
+    kernel_name = plan.last_kernel_name()   # what actually ran: ring, ring_small, panel, gather, dense_*+...
     # ---- roofline of the dominant kernel (this rank's launch) -------------------
     peak, peak_kind = hbm_peak()
     alg_bytes = synth.algorithmic_bytes(shard.n_rows, b - a, K, m_nz_local, n_nz_local)
     kernel_ms = statistics.mean(step_ms)
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic = ncu_traffic(p["workload"], kernel_name) if world == 1 else None
+    capture = ncu_traffic(p["workload"], kernel_name) if world == 1 else None
+    traffic = capture["dram_bytes_per_launch"] if capture else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": alg_bytes,
                 "kernel_ms": kernel_ms, "kernel_ms_min": min(step_ms), "kernel_ms_median": statistics.median(step_ms),
                 "frac_of_nominal_8000": achieved / 8000.0,
-                "kernel": f"sddmm_{kernel_name}_kernel"}
-    if traffic:
-        roofline["dram_gbs"] = traffic / (kernel_ms * 1e-3) / 1e9
-        roofline["dram_frac"] = roofline["dram_gbs"] / peak
+                "kernel": kernel_name}
+    if capture:
+        # measured: the capture's bytes over the capture's own duration.  The same bytes over THIS run's
+        # kernel time is an estimate (another GPU, another day) and is labelled as one.
+        roofline["traffic_source"] = capture["source"]
+        roofline["traffic_scaled_from"] = capture.get("scaled_from")
+        roofline["dram_frac_at_capture"] = traffic / (capture["ncu_duration_ms"] * 1e-3) / 1e9 / peak
+        roofline["dram_frac_estimate_live"] = traffic / (kernel_ms * 1e-3) / 1e9 / peak
         roofline["traffic_ratio"] = traffic / alg_bytes
     gather_bytes = 4 * K * (b - a) + 4 * K * m_nz_local + 12 * (b - a) + 4 * (shard.n_rows + 1)
     roofline["gather_model_bytes"] = gather_bytes
@@ -382,6 +476,7 @@ def main():
 
     # ---- end to end through the C ABI with host buffers -------------------------
     e2e = None
+    hW = hH = hS = hP = None
     if not args.no_e2e:
         try:
             hW = torch.empty(l_W.shape, dtype=torch.float32, pin_memory=True).copy_(l_W)
@@ -431,6 +526,8 @@ def main():
             e2e = {"value": 2.0 * nnz * K / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                    "h2d_bytes_per_step": int(tb[0].item()), "d2h_bytes_per_step": int(tb[1].item()),
                    "ms_per_step": e2e_ms, "steps": n_e2e, "host_memory": "pinned",
+                   "outside_the_step": "the plan (binning pass, plan_ms) and the upload of the 8 nnz bytes of row and "
+                                       "column indices it keeps; the reference uploads indices inside sddmm_GPU",
                    "operand_bytes": int(tb[2].item())}
             # the host copy of the result is the one that is checked below
             P_check = hP
@@ -440,7 +537,26 @@ def main():
     else:
         P_check = None
 
-    # ---- CPU baseline on a bounded sample (rank 0, one GPU) and a spot check ----
+    # ---- parity with the CPU oracle, every rank, every world size ---------------
+    # >= 262,144 nonzeros in 256 evenly spaced blocks over the rank's whole slice; both the device-resident
+    # result and the host result of the end-to-end step are checked; a disagreement ends the run non-zero.
+    handle.sync()                                   # also reads the device status word of the FLAG_ASYNC calls
+    results = [P] + ([P_check] if P_check is not None else [])
+    worst, n_checked = oracle_sample_check(l_rows, l_cols, l_vals, l_W, H, results)
+    tp = torch.tensor([worst], device=device, dtype=torch.float64)
+    per_rank = [worst]
+    n_total = torch.tensor([n_checked], device=device, dtype=torch.int64)
+    if world > 1:
+        every = [torch.zeros_like(tp) for _ in range(world)]
+        dist.all_gather(every, tp)
+        per_rank = [float(x.item()) for x in every]
+        dist.all_reduce(n_total, op=dist.ReduceOp.SUM)
+    parity = {"max_scaled_err": max(per_rank), "n_checked": int(n_total.item()), "per_rank": per_rank,
+              "checked": "P resident" + (" and P from the end-to-end step" if P_check is not None else ""),
+              "tolerance": 1e-4, "oracle": "oracle/sddmm_oracle.c (fp32 sequential) + float64 magnitude scale"}
+    parity_failed = not (parity["max_scaled_err"] <= 1e-4)
+
+    # ---- CPU baseline on a bounded sample (rank 0, one GPU) ----------------------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cols_h, vals_h = cols.cpu().numpy(), vals.cpu().numpy()
@@ -452,17 +568,21 @@ def main():
         cpu_baseline = {"value": gflops, "unit": "GFLOP/s", "cores": cores, "kind": "port",
                         "sample": f"{n_used} nonzeros ({100.0 * n_used / nnz:.2f}% of nnz) from 64 evenly spaced "
                                   f"blocks, W rows compacted, H whole; best of 2"}
-        # spot check of the GPU result against the oracle on the first sampled nonzeros
-        import oracle
-        idx = sample_blocks(nnz, min(nnz, 40_000_000))[:200_000]
-        ref = oracle.cpu.sddmm_coo(r[:idx.shape[0]], c[:idx.shape[0]], Ws, H_h, v[:idx.shape[0]])
-        _, A = oracle.cpu.sddmm_coo_f64(r[:idx.shape[0]], c[:idx.shape[0]], Ws, H_h, v[:idx.shape[0]])
-        src = P_check if P_check is not None else P.cpu()
-        got = src.numpy()[idx].astype(np.float64)
-        worst = float(np.max(np.abs(got - ref) / np.maximum(np.maximum(np.abs(ref), A), 1e-30)))
-        cpu_baseline["spot_check_max_scaled_err"] = worst
-        if worst > 1e-4:
-            raise SystemExit(f"GPU result disagrees with the CPU oracle: scaled error {worst}")
+        del r, c, v, Ws, H_h, cols_h, vals_h
+
+    launches_main = handle.kernel_launches() - launches_before
+
+    # ---- the other configurations, briefly (one GPU) ----------------------------
+    also = None
+    if rank == 0 and world == 1 and not args.no_also and not parity_failed:
+        c4_pattern = (rows, cols, vals, M, N) if (args.workload == "c4" and not args.scale) else None
+        del W, H, l_W, P, hW, hH, hS, hP, P_check, results, l_rows, l_cols, l_vals
+        for key in ("W", "H", "rows", "cols", "vals"):
+            p.pop(key, None)
+        plan.close()
+        plan = None
+        torch.cuda.empty_cache()
+        also = run_also(handle, device, peak, c4_pattern, args)
 
     if rank == 0:
         line = {
@@ -478,14 +598,25 @@ def main():
                        "rank_ms_per_step": [round(x, 4) for x in rank_ms], "partition_row_cost": row_cost,
                        "dense_cells": info.n_dense_cells, "dense_cell_nnz": info.n_dense_nnz,
                        "hub_columns": info.n_hub_cols},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            # one launch per step, two when the plan split S into dense cells and a remainder
-            "gpu_launches": args.steps * (2 if (info.n_dense_cells > 0 and args.kernel == "auto") else 1),
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "parity": parity,
+            # counted by the library: kernels launched by sddmm_execute / sddmm_upload_rows on this rank from the
+            # first warm-up step to the end of the end-to-end steps (timed steps: one SDDMM kernel each, two when
+            # the plan split S into dense cells and a remainder)
+            "gpu_launches": launches_main,
+            "gpu_launches_timed_steps": args.steps * (2 if (info.n_dense_cells > 0 and args.kernel == "auto") else 1),
             "clocks": clocks.summary(),
         }
+        if also is not None:
+            line["also"] = also
         print(json.dumps(line), flush=True)
-    plan.close()
-    handle.close()
+    if parity_failed:
+        sys.stderr.write(f"bench.py: GPU result disagrees with the CPU oracle: {parity}\n")
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        raise SystemExit(3)
+    if plan is not None:
+        handle.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

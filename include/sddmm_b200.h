@@ -58,6 +58,7 @@ enum {
 /* ---- plan flags ---------------------------------------------------------- */
 #define SDDMM_PLAN_SKIP_VALIDATION 0x1u /* trust sortedness and bounds (the reference checks neither) */
 #define SDDMM_PLAN_DEVICE_INDICES  0x2u /* rows/cols are device pointers on the handle's device */
+#define SDDMM_PLAN_FORCE_H_CHUNKS  0x4u /* sddmm_dist_plan_coo: build and use the column-bucketed form even with a single rank (exercises the overlapped execute on one GPU; the broadcasts are no-ops) */
 
 typedef struct sddmm_handle_s *sddmm_handle_t;
 typedef struct sddmm_plan_s *sddmm_plan_t;
@@ -149,6 +150,12 @@ SDDMM_API int sddmm_last_kernel_ms(sddmm_plan_t p, float *ms);
  * "panel", "gather", "dense_tc+ring_small", ... (static storage).  The reference has one
  * kernel, comp_kernel_COO (HiPC18/src/kernel.h:2), and nothing to report. */
 SDDMM_API const char *sddmm_last_kernel_name(sddmm_plan_t p);
+
+/* Number of kernels sddmm_execute() and sddmm_upload_rows() have launched through this
+ * handle since it was created (SDDMM kernels, row uploads, operand transpositions; plan-time
+ * kernels are not counted).  The reference launches n_col_tiles * K/k_slice kernels per call
+ * (HiPC18/src/sddmm.cu:95-108). */
+SDDMM_API int sddmm_kernel_launches(sddmm_handle_t h, int64_t *n);
 
 /*
  * Wait for everything enqueued on the handle's stream and report the device
@@ -322,6 +329,97 @@ SDDMM_API int sddmm_partition_rows(int64_t M, int64_t nnz, const int32_t *rows,
 SDDMM_API int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_t *rows, int n_parts,
                                             int align_rows, double row_cost, int64_t *cuts,
                                             int64_t *nnz_cuts);
+
+/* ---- several GPUs ---------------------------------------------------------------
+ *
+ * Replaces the MPI program of the reference (HiPC18_mpi/sddmm.cu:139-351, launched as
+ * `mpiexec -n P -ppn 1 sddmm ...`, HiPC18_mpi/scripts/run_mpi.sh:14-22), which
+ * partitions by columns in make_CSC (HiPC18_mpi/util.h:100-135), uploads all of W and H
+ * on every rank (HiPC18_mpi/sddmm.cu:281-284) and uses MPI for barriers only.  Here a
+ * rank owns an nnz-balanced block of consecutive ROWS (sddmm_partition_rows) and H
+ * travels over NCCL (NVLink / NVSwitch) into every GPU's own memory.  NCCL is bound at
+ * run time; without it these entry points return SDDMM_NCCL_ERROR and the
+ * single-GPU ones are unaffected.
+ *
+ * Two forms: (1) one rank per process (or thread): sddmm_comm_* + sddmm_dist_*; the
+ * caller carries the 128-byte id from rank 0 to the others (any channel: a file, a
+ * socket, MPI, torch.distributed) as ncclGetUniqueId / ncclCommInitRank ask;
+ * (2) one process driving all GPUs from host arrays: sddmm_multi_*.
+ */
+#define SDDMM_COMM_ID_BYTES 128
+typedef struct sddmm_comm_s *sddmm_comm_t;
+typedef struct sddmm_dist_plan_s *sddmm_dist_plan_t;
+
+/* Fills id[SDDMM_COMM_ID_BYTES] (ncclGetUniqueId); call on one rank, hand the bytes to all. */
+SDDMM_API int sddmm_comm_unique_id(void *id);
+/* Joins the communicator on the handle's GPU (ncclCommInitRank; returns when all `world`
+ * ranks have called).  Owns a communication stream next to the handle's compute stream. */
+SDDMM_API int sddmm_comm_create(sddmm_handle_t h, const void *id, int rank, int world, sddmm_comm_t *out);
+SDDMM_API int sddmm_comm_destroy(sddmm_comm_t c);
+/* buf (count floats, device memory on every rank) <- root's buf; stream-ordered on
+ * cuda_stream (NULL: the handle's stream).  The reference has no collective. */
+SDDMM_API int sddmm_comm_broadcast(sddmm_comm_t c, float *buf, int64_t count, int root, void *cuda_stream);
+/* In place: rank r holds floats [r * count_per_rank, (r+1) * count_per_rank) of buf;
+ * afterwards every rank holds all world * count_per_rank (ncclAllGather). */
+SDDMM_API int sddmm_comm_all_gather(sddmm_comm_t c, float *buf, int64_t count_per_rank, void *cuda_stream);
+
+/*
+ * This rank's part of a plan over the WHOLE matrix (every rank passes the same row-sorted
+ * pattern, as every MPI rank of the reference parses the same file): rows are cut with
+ * sddmm_partition_rows (32-row alignment), the rank's block is planned like
+ * sddmm_plan_coo, and -- when h_chunks > 1 -- a second, column-bucketed plan is built
+ * for the execute that overlaps the H broadcast (h_chunks column ranges of S = blocks of
+ * consecutive rows of H).  flags: SDDMM_PLAN_*; with SDDMM_PLAN_DEVICE_INDICES rows and
+ * cols are device arrays (borrowed for the life of the plan).
+ */
+SDDMM_API int sddmm_dist_plan_coo(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const int32_t *rows,
+                                  const int32_t *cols, int K, int panel_rows_hint, int h_chunks, uint32_t flags,
+                                  sddmm_dist_plan_t *out);
+SDDMM_API int sddmm_dist_plan_destroy(sddmm_dist_plan_t p);
+/* The rank's rows [row_begin, row_end) and nonzeros [nnz_begin, nnz_end) of the input, and
+ * the number of H chunks in use.  Any output may be NULL. */
+SDDMM_API int sddmm_dist_plan_get_shard(sddmm_dist_plan_t p, int64_t *row_begin, int64_t *row_end, int64_t *nnz_begin,
+                                        int64_t *nnz_end, int32_t *n_chunks);
+/* The rank's single-GPU plan (for sddmm_plan_get_info, sddmm_plan_count_cols, ...); owned by p. */
+SDDMM_API sddmm_plan_t sddmm_dist_plan_local(sddmm_dist_plan_t p);
+
+#define SDDMM_DIST_H_RESIDENT     0x10000u /* H is already complete on every rank: no collective, plain execute */
+#define SDDMM_DIST_BROADCAST_ONLY 0x20000u /* only the chunked H broadcast (to time it on its own) */
+/*
+ * One SDDMM over the rank's block: W_local = the rank's rows of W, Sval_local / P_local =
+ * its slice of the nonzeros, H = a device array of N x K floats on every rank.  Without
+ * SDDMM_DIST_H_RESIDENT, root's H is broadcast inside the call in the plan's chunks on the
+ * communication stream while the nonzeros of the column ranges already received are
+ * computed (all operands must be device arrays).  SDDMM_FLAG_* as in sddmm_execute.
+ */
+SDDMM_API int sddmm_dist_execute(sddmm_dist_plan_t p, const float *W_local, float *H, const float *Sval_local,
+                                 float *P_local, int root, uint32_t flags);
+/* Of the last synchronous sddmm_dist_execute on this rank, in ms (CUDA events): the
+ * broadcast (first chunk enqueued -> last chunk arrived), the kernels when H was resident,
+ * and the whole call on the compute stream.  -1 where it does not apply. */
+SDDMM_API int sddmm_dist_last_times(sddmm_dist_plan_t p, float *bcast_ms, float *compute_ms, float *total_ms);
+
+typedef struct sddmm_multi_s *sddmm_multi_t;
+typedef struct sddmm_multi_plan_s *sddmm_multi_plan_t;
+/* One process, ndev GPUs (devices == NULL: 0 .. ndev-1): a handle, a host thread and a
+ * communicator per GPU. */
+SDDMM_API int sddmm_multi_create(const int *devices, int ndev, sddmm_multi_t *out);
+SDDMM_API int sddmm_multi_destroy(sddmm_multi_t m);
+SDDMM_API const char *sddmm_multi_last_error(sddmm_multi_t m);
+/* Host pattern (row-sorted COO); allocates every GPU's operand buffers. */
+SDDMM_API int sddmm_multi_plan_coo(sddmm_multi_t m, int64_t M, int64_t N, int64_t nnz, const int32_t *rows,
+                                   const int32_t *cols, int K, int panel_rows_hint, uint32_t flags,
+                                   sddmm_multi_plan_t *out);
+SDDMM_API int sddmm_multi_plan_destroy(sddmm_multi_plan_t p);
+/* row_cuts / nnz_cuts: ndev + 1 entries each (either may be NULL). */
+SDDMM_API int sddmm_multi_plan_get_cuts(sddmm_multi_plan_t p, int64_t *row_cuts, int64_t *nnz_cuts);
+/* W, H, Sval (or NULL), P: HOST arrays of the whole problem.  Every GPU uploads its rows
+ * of W, its S values and 1/ndev of H over its own PCIe link; the H slices are exchanged
+ * with one all-gather; P comes back in input order. */
+SDDMM_API int sddmm_multi_execute(sddmm_multi_plan_t p, const float *W, const float *H, const float *Sval, float *P,
+                                  uint32_t flags);
+/* Slowest GPU's kernel time of the last sddmm_multi_execute, in ms. */
+SDDMM_API int sddmm_multi_last_kernel_ms(sddmm_multi_plan_t p, float *ms);
 
 /* ---- Matrix Market I/O (host) -------------------------------------------- */
 

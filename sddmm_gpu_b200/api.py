@@ -27,13 +27,19 @@ FLAG_KERNEL_PANEL = 0x20
 FLAG_KERNEL_RING = 0x40
 PLAN_SKIP_VALIDATION = 0x1
 PLAN_DEVICE_INDICES = 0x2
+PLAN_FORCE_H_CHUNKS = 0x4
 
 EXPORTED_SYMBOLS = [
     "sddmm_status_string", "sddmm_create", "sddmm_destroy", "sddmm_last_error", "sddmm_set_stream",
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
-    "sddmm_last_kernel_name", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
+    "sddmm_last_kernel_name", "sddmm_kernel_launches", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
+    "sddmm_comm_unique_id", "sddmm_comm_create", "sddmm_comm_destroy", "sddmm_comm_broadcast", "sddmm_comm_all_gather",
+    "sddmm_dist_plan_coo", "sddmm_dist_plan_destroy", "sddmm_dist_plan_get_shard", "sddmm_dist_plan_local",
+    "sddmm_dist_execute", "sddmm_dist_last_times", "sddmm_multi_create", "sddmm_multi_destroy", "sddmm_multi_last_error",
+    "sddmm_multi_plan_coo", "sddmm_multi_plan_destroy", "sddmm_multi_plan_get_cuts", "sddmm_multi_execute",
+    "sddmm_multi_last_kernel_ms",
     "sddmm_mtx_close", "sddmm_mtx_open_ex", "sddmm_coo_save_binary", "sddmm_coo_sort_rows_gpu", "sddmm_gen_open", "sddmm_coo_is_row_sorted", "sddmm_mtx_write", "sddmm_coo_sort_rows",
 ]
 
@@ -82,9 +88,32 @@ def lib():
     L.sddmm_last_kernel_name.restype = C.c_char_p
     L.sddmm_last_kernel_name.argtypes = [vp]
     L.sddmm_sync.argtypes = [vp]
+    L.sddmm_kernel_launches.argtypes = [vp, C.POINTER(i64)]
     L.sddmm_check_result.argtypes = [vp, vp, vp, vp, vp, i64, C.c_double, C.POINTER(C.c_double), C.POINTER(i64),
                                      C.POINTER(i64)]
     L.sddmm_selftest_optin_cache.argtypes = []
+    L.sddmm_comm_unique_id.argtypes = [vp]
+    L.sddmm_comm_create.argtypes = [vp, vp, C.c_int, C.c_int, C.POINTER(vp)]
+    L.sddmm_comm_destroy.argtypes = [vp]
+    L.sddmm_comm_broadcast.argtypes = [vp, vp, i64, C.c_int, vp]
+    L.sddmm_comm_all_gather.argtypes = [vp, vp, i64, vp]
+    L.sddmm_dist_plan_coo.argtypes = [vp, i64, i64, i64, vp, vp, C.c_int, C.c_int, C.c_int, u32, C.POINTER(vp)]
+    L.sddmm_dist_plan_destroy.argtypes = [vp]
+    L.sddmm_dist_plan_get_shard.argtypes = [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
+                                            C.POINTER(i32)]
+    L.sddmm_dist_plan_local.restype = vp
+    L.sddmm_dist_plan_local.argtypes = [vp]
+    L.sddmm_dist_execute.argtypes = [vp, vp, vp, vp, vp, C.c_int, u32]
+    L.sddmm_dist_last_times.argtypes = [vp, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.sddmm_multi_create.argtypes = [vp, C.c_int, C.POINTER(vp)]
+    L.sddmm_multi_destroy.argtypes = [vp]
+    L.sddmm_multi_last_error.restype = C.c_char_p
+    L.sddmm_multi_last_error.argtypes = [vp]
+    L.sddmm_multi_plan_coo.argtypes = [vp, i64, i64, i64, vp, vp, C.c_int, C.c_int, u32, C.POINTER(vp)]
+    L.sddmm_multi_plan_destroy.argtypes = [vp]
+    L.sddmm_multi_plan_get_cuts.argtypes = [vp, vp, vp]
+    L.sddmm_multi_execute.argtypes = [vp, vp, vp, vp, vp, u32]
+    L.sddmm_multi_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
     L.sddmm_last_transfer_bytes.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.sddmm_plan_used_lines.argtypes = [vp, C.c_int, C.POINTER(vp), C.POINTER(i64)]
     L.sddmm_upload_rows.argtypes = [vp, vp, vp, vp, i64, C.c_int, vp]
@@ -198,6 +227,12 @@ class Handle:
         """cuda_stream: integer cudaStream_t (e.g. torch.cuda.current_stream().cuda_stream) or None."""
         self._check(lib().sddmm_set_stream(self._h, cuda_stream))
         self._explicit_stream = cuda_stream is not None
+
+    def kernel_launches(self):
+        """Kernels launched through this handle by execute() / upload_rows() so far."""
+        n = C.c_int64()
+        self._check(lib().sddmm_kernel_launches(self._h, C.byref(n)))
+        return n.value
 
     def sync(self):
         """Wait for the handle's stream; raises SddmmError(DEVICE_TIMEOUT) if a bounded device-side wait of
@@ -332,6 +367,139 @@ class Plan:
         out["ntile_c"] = ntile_c
         out["max_active_block"] = max_blk
         return out
+
+
+COMM_ID_BYTES = 128
+DIST_H_RESIDENT = 0x10000
+DIST_BROADCAST_ONLY = 0x20000
+
+
+def comm_unique_id():
+    """128 bytes that rank 0 creates and every rank passes to Comm() (ncclGetUniqueId)."""
+    buf = C.create_string_buffer(COMM_ID_BYTES)
+    st = lib().sddmm_comm_unique_id(buf)
+    if st != OK:
+        raise SddmmError(st, "NCCL is not available in this process")
+    return buf.raw
+
+
+class Comm:
+    """This rank's end of an NCCL communicator on the handle's GPU (sddmm_comm_create)."""
+
+    def __init__(self, handle, unique_id, rank, world):
+        self.handle, self.rank, self.world = handle, rank, world
+        self._c = C.c_void_p()
+        handle._check(lib().sddmm_comm_create(handle._h, unique_id, rank, world, C.byref(self._c)))
+
+    def close(self):
+        if self._c:
+            lib().sddmm_comm_destroy(self._c)
+            self._c = None
+
+    def broadcast(self, buf, root=0, cuda_stream=None):
+        self.handle._follow_torch_stream(buf)
+        self.handle._check(lib().sddmm_comm_broadcast(self._c, _ptr(buf), buf.numel(), root, cuda_stream))
+
+    def all_gather(self, buf, count_per_rank, cuda_stream=None):
+        """In place: rank r's floats [r * count_per_rank, (r + 1) * count_per_rank) of buf go to every rank."""
+        self.handle._follow_torch_stream(buf)
+        self.handle._check(lib().sddmm_comm_all_gather(self._c, _ptr(buf), count_per_rank, cuda_stream))
+
+    def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, h_chunks=1, flags=0):
+        """This rank's part of a plan over the whole matrix (sddmm_dist_plan_coo)."""
+        is_dev = _is_cuda_tensor(rows)
+        if is_dev:
+            flags |= PLAN_DEVICE_INDICES
+        p = C.c_void_p()
+        self.handle._follow_torch_stream(rows, cols)
+        self.handle._check(lib().sddmm_dist_plan_coo(self._c, M, N, int(rows.shape[0]), _ptr(rows), _ptr(cols), K,
+                                                     panel_rows_hint, h_chunks, flags, C.byref(p)))
+        return DistPlan(self, p, (rows, cols) if is_dev else None)
+
+
+class DistPlan:
+    def __init__(self, comm, p, keep):
+        self.comm, self._p, self._keep = comm, p, keep
+        rb, re_, nb, ne, nc = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64(), C.c_int32()
+        comm.handle._check(lib().sddmm_dist_plan_get_shard(p, C.byref(rb), C.byref(re_), C.byref(nb), C.byref(ne),
+                                                           C.byref(nc)))
+        self.row_begin, self.row_end, self.nnz_begin, self.nnz_end = rb.value, re_.value, nb.value, ne.value
+        self.n_chunks = nc.value
+        # the rank's single-GPU plan, owned by the distributed plan (never closed on its own)
+        self.local = Plan(comm.handle, C.c_void_p(lib().sddmm_dist_plan_local(p)), self.nnz_end - self.nnz_begin, None)
+        self.local.close = lambda: None
+
+    def close(self):
+        if self._p:
+            self.local._p = None
+            lib().sddmm_dist_plan_destroy(self._p)
+            self._p = None
+
+    def execute(self, W_local, H, P_local, Sval_local=None, root=0, flags=0):
+        """flags: FLAG_* | DIST_H_RESIDENT | DIST_BROADCAST_ONLY (sddmm_dist_execute)."""
+        h = self.comm.handle
+        h._follow_torch_stream(W_local, H, P_local, Sval_local)
+        h._check(lib().sddmm_dist_execute(self._p, _ptr(W_local), _ptr(H), _ptr(Sval_local), _ptr(P_local), root, flags))
+
+    def last_times(self):
+        """(broadcast ms, kernel ms with H resident, whole call ms) of the last synchronous execute."""
+        a, b, c = C.c_float(), C.c_float(), C.c_float()
+        self.comm.handle._check(lib().sddmm_dist_last_times(self._p, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+
+class MultiGpu:
+    """One process driving several GPUs from host arrays (sddmm_multi_*)."""
+
+    def __init__(self, devices):
+        devices = list(devices)
+        arr = (C.c_int * len(devices))(*devices)
+        self._m = C.c_void_p()
+        st = lib().sddmm_multi_create(arr, len(devices), C.byref(self._m))
+        if st != OK:
+            self._m = None
+            raise SddmmError(st)
+        self.devices = devices
+
+    def _check(self, st):
+        if st != OK:
+            raise SddmmError(st, lib().sddmm_multi_last_error(self._m).decode())
+
+    def close(self):
+        if self._m:
+            lib().sddmm_multi_destroy(self._m)
+            self._m = None
+
+    def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, flags=0):
+        p = C.c_void_p()
+        self._check(lib().sddmm_multi_plan_coo(self._m, M, N, int(rows.shape[0]), _ptr(rows), _ptr(cols), K,
+                                               panel_rows_hint, flags, C.byref(p)))
+        return MultiPlan(self, p)
+
+
+class MultiPlan:
+    def __init__(self, multi, p):
+        self.multi, self._p = multi, p
+
+    def close(self):
+        if self._p:
+            lib().sddmm_multi_plan_destroy(self._p)
+            self._p = None
+
+    def cuts(self):
+        n = len(self.multi.devices)
+        rc, nc = np.zeros(n + 1, np.int64), np.zeros(n + 1, np.int64)
+        self.multi._check(lib().sddmm_multi_plan_get_cuts(self._p, rc.ctypes.data, nc.ctypes.data))
+        return rc, nc
+
+    def execute(self, W, H, P, Sval=None, flags=0):
+        """W, H, Sval, P: host arrays of the whole problem."""
+        self.multi._check(lib().sddmm_multi_execute(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P), flags))
+
+    def last_kernel_ms(self):
+        ms = C.c_float()
+        self.multi._check(lib().sddmm_multi_last_kernel_ms(self._p, C.byref(ms)))
+        return ms.value
 
 
 NOALLOC_MAX_COLS = 8 * 1024 * 1024

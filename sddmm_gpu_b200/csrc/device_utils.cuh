@@ -100,7 +100,10 @@ __device__ __forceinline__ unsigned long long globaltimer_ns()
 // time (every try_wait may block for a hardware-defined slice before it answers),
 // so the loop also reads the nanosecond timer every 64 polls and gives up once the
 // budget is spent; the poll limit stays as a backstop should the timer stand still.
-constexpr unsigned long long MBAR_WAIT_BUDGET_NS = 2000000000ull;  // 2 s
+#ifndef SDDMM_WAIT_BUDGET_MS
+#define SDDMM_WAIT_BUDGET_MS 500
+#endif
+constexpr unsigned long long MBAR_WAIT_BUDGET_NS = SDDMM_WAIT_BUDGET_MS * 1000000ull;  // 0.5 s: a thousand times any legitimate wait
 struct WaitClock {
     unsigned long long start = 0;
     __device__ __forceinline__ bool expired(int it, unsigned long long budget_ns = MBAR_WAIT_BUDGET_NS)

@@ -20,80 +20,7 @@
 
 using namespace sddmm;
 
-// Host-operand pipeline: S is cut into at most this many chunks of consecutive nonzeros.
-#define SDDMM_PIPE_MAX_CHUNKS 16
-
-struct sddmm_handle_s {
-    int device = 0;
-    int sm_count = 0;
-    size_t smem_optin = 0;
-    cudaStream_t own_stream = nullptr;
-    cudaStream_t stream = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    int *d_status = nullptr;  // device status word of bounded waits
-    unsigned long long *d_work_counter = nullptr;  // dynamic work distribution of the ring kernel
-    int *h_status = nullptr;  // pinned mirror
-    std::string last_error;
-    // dense cells: 0 = fp32 FMA, 1 = 3xTF32 on mma.sync, 2 = 3xTF32 on tcgen05 / tensor memory (SDDMM_DENSE_TENSOR)
-    int dense_mode = 2;
-    // pipelined execution with host operands: compute and download streams, one
-    // "uploaded" and one "computed" event per chunk (created on first use)
-    cudaStream_t pipe_compute = nullptr, pipe_download = nullptr;
-    cudaEvent_t pipe_uploaded[SDDMM_PIPE_MAX_CHUNKS] = {};
-    cudaEvent_t pipe_started[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_computed[SDDMM_PIPE_MAX_CHUNKS] = {};  // timing events
-    cudaEvent_t pipe_joined = nullptr;
-    bool pipeline = true;  // SDDMM_PIPELINE=0 keeps upload, kernel and download strictly one after the other
-    // pipelined calls whose host operands are page-locked and mapped upload only the rows of
-    // W and H that a nonzero touches, read by the GPU (SDDMM_SPARSE_UPLOAD=0: whole arrays by cudaMemcpy)
-    bool sparse_upload = true;
-    int upload_ctas = 0;  // CTAs of the upload kernel (SDDMM_UPLOAD_CTAS; default half the SMs)
-};
-
-struct sddmm_plan_s {
-    sddmm_handle_s *h = nullptr;
-    int64_t M = 0, N = 0, nnz = 0;
-    int K = 0;
-    int col_tile = 0;     // == N (clamped) when there is a single column tile
-    int n_col_tiles = 1;
-    PanelConfig cfg{};
-    // pattern, input order
-    int32_t *d_rows = nullptr, *d_cols = nullptr;
-    bool owns_rows = true, owns_cols = true;
-    // pattern, tiled order (only when n_col_tiles > 1)
-    int32_t *d_rows_t = nullptr, *d_cols_t = nullptr, *d_perm = nullptr;
-    int64_t *d_row_ptr = nullptr;
-    WorkItem *d_items = nullptr;
-    int64_t n_items = 0;
-    int32_t *d_item_rows = nullptr;  // distinct rows of every item, concatenated
-    int32_t *d_cols_hint = nullptr;  // processing-order columns with hub marks (ring kernel), or null
-    // dense cells + row-sorted remainder (single-tile plans of locally dense matrices)
-    DensePlan dense;
-    WorkItem *d_items_s = nullptr;
-    int64_t n_items_s = 0;
-    int32_t *d_item_rows_s = nullptr;
-    int64_t n_item_rows_s = 0;
-    int64_t n_hub_cols = 0;
-    int64_t n_item_rows = 0;
-    int64_t n_nonempty_rows = 0, n_nonempty_cols = -1;
-    // staging for host operands (allocated on first use)
-    float *d_W = nullptr, *d_H = nullptr, *d_S = nullptr, *d_P = nullptr;
-    float *d_Wt = nullptr, *d_Ht = nullptr;  // device copies of K-major host operands, before their transposition
-    int64_t device_bytes = 0;
-    float plan_ms = 0.f, last_ms = -1.f;
-    // chunks of the host-operand pipeline (0 = not pipelined): nonzeros
-    // [pipe_nnz[i], pipe_nnz[i+1]) touch the rows pipe_row_first[i] .. pipe_row_last[i] of W
-    int n_pipe = 0;
-    int64_t pipe_nnz[SDDMM_PIPE_MAX_CHUNKS + 1] = {};
-    int32_t pipe_row_first[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_row_last[SDDMM_PIPE_MAX_CHUNKS] = {};
-    // rows of W chunk i uploads: [pipe_w_begin[i], pipe_w_end[i]) (empty when an earlier chunk brought them),
-    // = entries [pipe_list_begin[i], pipe_list_begin[i+1]) of the used-row list
-    int64_t pipe_w_begin[SDDMM_PIPE_MAX_CHUNKS] = {}, pipe_w_end[SDDMM_PIPE_MAX_CHUNKS] = {};
-    int64_t pipe_list_begin[SDDMM_PIPE_MAX_CHUNKS + 1] = {};
-    int32_t *d_used_rows = nullptr, *d_used_cols = nullptr;  // ascending ids of the rows / columns holding a nonzero
-    int64_t n_used_rows = 0, n_used_cols = 0;
-    int64_t last_h2d_bytes = 0, last_d2h_bytes = 0;  // moved by the last sddmm_execute
-    const char *last_kernel = "none";                // kernels the last sddmm_execute launched
-};
+#include "engine_internal.hpp"
 
 namespace {
 
@@ -110,6 +37,13 @@ int fail_cuda(sddmm_handle_s *h, cudaError_t e, const char *what)
     do {                                                    \
         cudaError_t _e = (expr);                            \
         if (_e != cudaSuccess) return fail_cuda((h), _e, #expr); \
+    } while (0)
+
+// A kernel launch: counted per handle (sddmm_kernel_launches).
+#define LAUNCH_TRY(h, expr)   \
+    do {                      \
+        CUDA_TRY(h, expr);    \
+        ++(h)->n_launches;    \
     } while (0)
 
 bool is_device_ptr(const void *p)
@@ -191,6 +125,15 @@ cudaError_t ensure_pipeline(sddmm_handle_s *h)
     }
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_joined, cudaEventDisableTiming);
     return e;
+}
+
+// The gather kernel for ring-supported K.
+cudaError_t launch_rows_gather(sddmm_handle_s *h, const int32_t *rows, const int32_t *cols, const int32_t *perm,
+                               const float *sval, const float *W, const float *H, float *P, int64_t nnz, int K,
+                               bool cols_hinted, cudaStream_t stream)
+{
+    return launch_ring(rows, cols, perm, sval, W, H, P, nnz, K, cols_hinted, h->sm_count, h->d_work_counter, h->d_status,
+                       stream);
 }
 
 // After a synchronising point: turn the device status word into a status code.
@@ -556,12 +499,12 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             src = p->d_Ht;
         }
         if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
-        CUDA_TRY(h, launch_transpose_operand(src, p->d_H, p->N, p->K, s));
+        LAUNCH_TRY(h, launch_transpose_operand(src, p->d_H, p->N, p->K, s));
         dH = p->d_H;
     } else if (!h_dev) {
         if (!p->d_H) CUDA_TRY(h, dev_alloc(p, &p->d_H, (size_t)p->N * p->K));
         if (H_mapped) {
-            CUDA_TRY(h, launch_upload_rows(H_mapped, p->d_H, p->d_used_cols, p->n_used_cols, p->K, h->upload_ctas, s));
+            LAUNCH_TRY(h, launch_upload_rows(H_mapped, p->d_H, p->d_used_cols, p->n_used_cols, p->K, h->upload_ctas, s));
             p->last_h2d_bytes += (int64_t)sizeof(float) * p->n_used_cols * p->K;
         } else {
             CUDA_TRY(h, cudaMemcpyAsync(p->d_H, H, hbytes, cudaMemcpyHostToDevice, s));
@@ -578,7 +521,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             src = p->d_Wt;
         }
         if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
-        CUDA_TRY(h, launch_transpose_operand(src, p->d_W, p->M, p->K, s));
+        LAUNCH_TRY(h, launch_transpose_operand(src, p->d_W, p->M, p->K, s));
         dW = p->d_W;
     } else if (!w_dev) {
         if (!p->d_W) CUDA_TRY(h, dev_alloc(p, &p->d_W, (size_t)p->M * p->K));
@@ -615,7 +558,7 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             const int64_t r0 = p->pipe_w_begin[i], r1 = p->pipe_w_end[i];
             if (W_mapped) {
                 const int64_t l0 = p->pipe_list_begin[i], ln = p->pipe_list_begin[i + 1] - l0;
-                CUDA_TRY(h, launch_upload_rows(W_mapped, p->d_W, p->d_used_rows + l0, ln, p->K, h->upload_ctas, s));
+                LAUNCH_TRY(h, launch_upload_rows(W_mapped, p->d_W, p->d_used_rows + l0, ln, p->K, h->upload_ctas, s));
                 p->last_h2d_bytes += (int64_t)sizeof(float) * ln * p->K;
             } else if (r1 > r0) {
                 CUDA_TRY(h, cudaMemcpyAsync(p->d_W + r0 * p->K, W + r0 * p->K, sizeof(float) * (size_t)(r1 - r0) * p->K,
@@ -627,9 +570,8 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             CUDA_TRY(h, cudaEventRecord(h->pipe_uploaded[i], s));
             CUDA_TRY(h, cudaStreamWaitEvent(h->pipe_compute, h->pipe_uploaded[i], 0));
             CUDA_TRY(h, cudaEventRecord(h->pipe_started[i], h->pipe_compute));
-            CUDA_TRY(h, launch_ring(p->d_rows + n0, cols_p + n0, nullptr, dS ? dS + n0 : nullptr, dW, dH, dP + n0, cnt, p->K,
-                                    p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status,
-                                    h->pipe_compute));
+            LAUNCH_TRY(h, launch_rows_gather(h, p->d_rows + n0, cols_p + n0, nullptr, dS ? dS + n0 : nullptr, dW, dH, dP + n0,
+                                             cnt, p->K, p->d_cols_hint != nullptr, h->pipe_compute));
             CUDA_TRY(h, cudaEventRecord(h->pipe_computed[i], h->pipe_compute));
             if (!p_dev) {
                 CUDA_TRY(h, cudaStreamWaitEvent(h->pipe_download, h->pipe_computed[i], 0));
@@ -666,26 +608,26 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
                                                     : (h->dense_mode == 1 ? "dense_mma_sync+ring_small" : "dense_fma+ring_small");
         }
         if (h->dense_mode == 2)
-            CUDA_TRY(h, launch_dense_cells_tc(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
+            LAUNCH_TRY(h, launch_dense_cells_tc(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
                                               p->dense.row_base, p->dense.dense_rows, p->dense.n_dense_rows,
                                               p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP, p->M, p->N, p->K,
                                               h->sm_count, h->d_status, s));
         else
-            CUDA_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
+            LAUNCH_TRY(h, launch_dense_cells(p->dense.cells, p->dense.n_cells, p->dense.idx, p->dense.rc, p->dense.row_mask,
                                            p->dense.row_base, p->dense.dense_rows, p->dense.n_dense_rows,
                                            p->dense.dense_cols, p->dense.n_dense_cols, dS, dW, dH, dP, p->M, p->N, p->K,
                                            h->dense_mode == 1, h->sm_count, s));
         if (p->dense.n_sparse > 0) {
             if (ring_supports(p->K))
-                CUDA_TRY(h, launch_ring(p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP, p->dense.n_sparse,
-                                        p->K, false, h->sm_count, h->d_work_counter, h->d_status, s));
+                LAUNCH_TRY(h, launch_rows_gather(h, p->dense.rows_s, p->dense.cols_s, p->dense.perm_s, dS, dW, dH, dP,
+                                                 p->dense.n_sparse, p->K, false, s));
             else
-                CUDA_TRY(h, launch_panel(p->d_items_s, p->n_items_s, p->d_item_rows_s, p->dense.rows_s, p->dense.cols_s,
+                LAUNCH_TRY(h, launch_panel(p->d_items_s, p->n_items_s, p->d_item_rows_s, p->dense.rows_s, p->dense.cols_s,
                                          p->dense.perm_s, dS, dW, dH, dP, p->K, p->cfg, h->sm_count, h->d_status, s));
         }
     } else if (use_gather) {
         p->last_kernel = "gather";
-        CUDA_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
+        LAUNCH_TRY(h, launch_gather(p->d_rows, p->d_cols, dS, dW, dH, dP, p->nnz, p->K, h->sm_count, s));
     } else {
         const bool tiled = p->d_perm != nullptr;
         const int32_t *rows_p = tiled ? p->d_rows_t : p->d_rows;
@@ -701,10 +643,10 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
         }
         p->last_kernel = use_ring ? ring_name : "panel";
         if (use_ring)
-            CUDA_TRY(h, launch_ring(rows_p, p->d_cols_hint ? p->d_cols_hint : cols_p, perm, dS, dW, dH, dP, p->nnz, p->K,
-                                    p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status, s));
+            LAUNCH_TRY(h, launch_rows_gather(h, rows_p, p->d_cols_hint ? p->d_cols_hint : cols_p, perm, dS, dW, dH, dP, p->nnz,
+                                             p->K, p->d_cols_hint != nullptr, s));
         else
-            CUDA_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K,
+            LAUNCH_TRY(h, launch_panel(p->d_items, p->n_items, p->d_item_rows, rows_p, cols_p, perm, dS, dW, dH, dP, p->K,
                                      p->cfg, h->sm_count, h->d_status, s));
     }
     CUDA_TRY(h, cudaEventRecord(h->ev1, s));
@@ -817,7 +759,7 @@ int sddmm_upload_rows(sddmm_handle_t h, const float *host, float *dev, const int
         h->last_error = "sddmm_upload_rows: dev and d_row_ids must be device memory, both arrays 16-byte aligned";
         return SDDMM_INVALID_ARG;
     }
-    CUDA_TRY(h, launch_upload_rows(mapped, dev, d_row_ids, n_rows, K, h->upload_ctas,
+    LAUNCH_TRY(h, launch_upload_rows(mapped, dev, d_row_ids, n_rows, K, h->upload_ctas,
                                    cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
     return SDDMM_OK;
 }
@@ -827,6 +769,13 @@ int sddmm_last_transfer_bytes(sddmm_plan_t p, int64_t *h2d_bytes, int64_t *d2h_b
     if (!p) return SDDMM_INVALID_ARG;
     if (h2d_bytes) *h2d_bytes = p->last_h2d_bytes;
     if (d2h_bytes) *d2h_bytes = p->last_d2h_bytes;
+    return SDDMM_OK;
+}
+
+int sddmm_kernel_launches(sddmm_handle_t h, int64_t *n)
+{
+    if (!h || !n) return SDDMM_INVALID_ARG;
+    *n = h->n_launches;
     return SDDMM_OK;
 }
 

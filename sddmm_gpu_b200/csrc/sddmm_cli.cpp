@@ -25,6 +25,10 @@
 //                      and COO CPU paths do (default: P = S o (W H^T))
 //   --gather           use the planless gather kernel
 //   --device D         CUDA device (default 0)
+//   --gpus N           split S into N nnz-balanced row blocks over GPUs 0 .. N-1 of this box (one host
+//                      thread and one NCCL rank per GPU, H exchanged over NVLink); what the reference
+//                      does with `mpiexec -n N` (HiPC18_mpi/scripts/run_mpi.sh).  The printed time is the
+//                      slowest GPU's kernel time
 //   --dump-p FILE      write P (float32, input nonzero order) to FILE
 //   --json FILE        write a small JSON report: ms, GFLOP/s, the kernels that ran, plan sizes,
 //                      GPU count, host cores and the roofline figures (algorithmic bytes of the
@@ -85,7 +89,7 @@ int main(int argc, char **argv)
 {
     if (argc < 5) {
         std::fprintf(stderr, "usage: %s input.mtx K tile_size_X tile_size_Y [--iters N] [--warmup N] "
-                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE] [--save-bin FILE] [--sort] [--expand-symmetric] [--check] [--seed S] [--hbm-gbs X]\n"
+                             "[--no-scale-by-s] [--gather] [--device D] [--dump-p FILE] [--json FILE] [--write-mtx FILE] [--save-bin FILE] [--gpus N] [--sort] [--expand-symmetric] [--check] [--seed S] [--hbm-gbs X]\n"
                              "       input may be gen:c1..c5 | gen:uniform:M:N:density | gen:zipf:M:N:nnz | "
                              "gen:rmat:scale:edge_factor | gen:band:M:half_width:g [:seed=S]\n", argv[0]);
         return 2;
@@ -94,7 +98,7 @@ int main(int argc, char **argv)
     const int K = std::atoi(argv[2]);
     const int panel_rows = std::atoi(argv[3]);  // tile_sizeY / actv_row_size in the reference
     const int col_tile = std::atoi(argv[4]);    // tile_sizeX in the reference
-    int iters = 1, warmup = 0, device = 0;
+    int iters = 1, warmup = 0, device = 0, gpus = 1;
     bool scale = true, gather = false;
     const char *dump_p = nullptr, *json = nullptr, *write_mtx = nullptr, *save_bin = nullptr;
     bool sort_input = false, check = false, have_seed = false;
@@ -113,6 +117,7 @@ int main(int argc, char **argv)
         if (a == "--iters") iters = std::atoi(need("--iters"));
         else if (a == "--warmup") warmup = std::atoi(need("--warmup"));
         else if (a == "--device") device = std::atoi(need("--device"));
+        else if (a == "--gpus") gpus = std::atoi(need("--gpus"));
         else if (a == "--no-scale-by-s") scale = false;
         else if (a == "--scale-by-s") scale = true;
         else if (a == "--gather") gather = true;
@@ -181,6 +186,39 @@ int main(int argc, char **argv)
         initial(H, N, K);
     }
 
+    const uint32_t flags = gather ? SDDMM_FLAG_KERNEL_GATHER : 0u;
+    const float *sval = scale ? vals.data() : nullptr;
+    double multi_ms = -1.0;
+    if (gpus > 1) {
+        // several GPUs: one rank per GPU inside this process
+        sddmm_multi_t multi = nullptr;
+        st = sddmm_multi_create(nullptr, gpus, &multi);
+        if (st != SDDMM_OK) {
+            sddmm_destroy(h);
+            return die("creating the multi-GPU engine", st, "");
+        }
+        sddmm_multi_plan_t mplan = nullptr;
+        st = sddmm_multi_plan_coo(multi, M, N, nnz, rows.data(), cols.data(), K, panel_rows, 0, &mplan);
+        double total = 0;
+        for (int it = 0; st == SDDMM_OK && it < warmup + iters; ++it) {
+            st = sddmm_multi_execute(mplan, W.data(), H.data(), sval, P.data(), flags);
+            float ms1 = 0;
+            sddmm_multi_last_kernel_ms(mplan, &ms1);
+            if (it >= warmup) total += ms1;
+        }
+        if (st != SDDMM_OK) {
+            int rc = die("running on several GPUs", st, sddmm_multi_last_error(multi));
+            sddmm_multi_plan_destroy(mplan);
+            sddmm_multi_destroy(multi);
+            sddmm_destroy(h);
+            return rc;
+        }
+        multi_ms = total / iters;
+        sddmm_multi_plan_destroy(mplan);
+        sddmm_multi_destroy(multi);
+    }
+
+    // the single-GPU plan: the whole run with one GPU; with several, what --check and the report read
     sddmm_plan_t plan = nullptr;
     st = sddmm_plan_coo(h, M, N, nnz, rows.data(), cols.data(), K, panel_rows, col_tile, 0, &plan);
     if (st != SDDMM_OK) {
@@ -188,10 +226,9 @@ int main(int argc, char **argv)
         sddmm_destroy(h);
         return rc;
     }
-    const uint32_t flags = gather ? SDDMM_FLAG_KERNEL_GATHER : 0u;
-    const float *sval = scale ? vals.data() : nullptr;
     double total_ms = 0;
-    for (int it = 0; it < warmup + iters; ++it) {
+    // with several GPUs P already holds the result that is reported, dumped and checked
+    for (int it = 0; it < (gpus > 1 ? 0 : warmup + iters); ++it) {
         st = sddmm_execute(plan, W.data(), H.data(), sval, P.data(), flags);
         if (st != SDDMM_OK) {
             int rc = die("executing", st, sddmm_last_error(h));
@@ -203,12 +240,12 @@ int main(int argc, char **argv)
         sddmm_last_kernel_ms(plan, &ms);
         if (it >= warmup) total_ms += ms;
     }
-    const double ms = total_ms / iters;
+    const double ms = gpus > 1 ? multi_ms : total_ms / iters;
     std::printf("\nTime for SDDMM with K = %d : %g ms\n", K, ms);
 
     sddmm_plan_info info;
     sddmm_plan_get_info(plan, &info);
-    const std::string kernel_name = sddmm_last_kernel_name(plan);
+    const std::string kernel_name = gpus > 1 ? "row blocks over several GPUs" : sddmm_last_kernel_name(plan);
     double check_err = -1.0;
     long long check_n = 0, check_bad = 0;
     if (check && nnz > 0) {
@@ -241,10 +278,10 @@ int main(int argc, char **argv)
         const double alg_bytes = 4.0 * K * (double)(info.n_nonempty_rows + n_cols_used) + 12.0 * (double)nnz + 4.0 * (double)(M + 1);
         const double achieved = ms > 0 ? alg_bytes / (ms * 1e6) : 0.0;
         std::fprintf(o, "{\"roofline\": {\"bound\": \"hbm\", \"algorithmic_bytes\": %.0f, \"achieved_gbs\": %.3f, \"peak_gbs\": %s, "
-                        "\"frac\": %s}, \"gpus\": 1, \"host_cores\": %u, \"check\": {\"ran\": %s, \"n\": %lld, \"bad\": %lld, "
+                        "\"frac\": %s}, \"gpus\": %d, \"host_cores\": %u, \"check\": {\"ran\": %s, \"n\": %lld, \"bad\": %lld, "
                         "\"max_scaled_err\": %.6g}, ",
                      alg_bytes, achieved, hbm_gbs > 0 ? std::to_string(hbm_gbs).c_str() : "null",
-                     hbm_gbs > 0 ? std::to_string(achieved / hbm_gbs).c_str() : "null", std::thread::hardware_concurrency(),
+                     hbm_gbs > 0 ? std::to_string(achieved / hbm_gbs / gpus).c_str() : "null", gpus, std::thread::hardware_concurrency(),
                      check ? "true" : "false", check_n, check_bad, check_err);
         std::fprintf(o,
                      "\"rows\": %lld, \"cols\": %lld, \"nnz\": %lld, \"K\": %d, \"kernel_ms\": %.6f, "

@@ -16,6 +16,7 @@ pytestmark = pytest.mark.gpu
 
 KERNELS = {"panel": api.FLAG_KERNEL_PANEL, "gather": api.FLAG_KERNEL_GATHER, "ring": api.FLAG_KERNEL_RING}
 RING_K = (32, 64, 128, 256, 512, 1024)
+LONG_ROW_K = (256, 512, 1024)
 
 
 def kernels_for(K):
@@ -243,6 +244,23 @@ def test_benchmark_configs(engine, name, kernel):
                        p["panel_rows"], p["col_tile"])
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
     assert info.nnz == p["rows"].shape[0]
+
+
+@pytest.mark.parametrize("K", LONG_ROW_K)
+def test_long_row_ring_shapes(engine, K):
+    """The TMA ring kernel (K = 256, 512, 1024) on inputs that exercise its edges: fewer nonzeros than one
+    group, a last group that is not full, sizes around a block of groups, the column-tile permutation,
+    scaled and unscaled."""
+    rng = np.random.default_rng(100 + K)
+    for M, N, nnz, col_tile in ((7, 9, 5, 0), (300, 200, 8191, 0), (300, 200, 8192, 0), (2000, 1500, 70001, 0),
+                                (300, 200, 9000, 64)):
+        rows, cols = random_coo(rng, M, N, nnz, empty_rows=[1, 2])
+        vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+        W = rng.standard_normal((M, K)).astype(np.float32)
+        H = rng.standard_normal((N, K)).astype(np.float32)
+        for sv in (vals, None):
+            P, _ = run_plan(engine, M, N, rows, cols, W, H, sv, KERNELS["ring"], 0, col_tile)
+            assert_parity(P, rows, cols, W, H, sv)
 
 
 def test_repeatable_and_reusable_plan(engine):
