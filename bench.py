@@ -391,29 +391,38 @@ def main():
     kflag = {"auto": 0, "ring": api.FLAG_KERNEL_RING, "panel": api.FLAG_KERNEL_PANEL,
              "gather": api.FLAG_KERNEL_GATHER}[args.kernel]
 
-    # ---- sharding (identity at one GPU) --------------------------------------
-    rows_host = rows.cpu().numpy()
-    row_cost = float(os.environ.get("SDDMM_PART_ROW_COST", "0"))
-    shard = multi_gpu.make_shard(M, rows_host, world, rank, align_rows=32, row_cost=row_cost)
-    a, b = shard.nnz_begin, shard.nnz_end
-    l_rows = (rows[a:b] - shard.row_begin).contiguous()
+    # ---- sharding through the C ABI (identity at one GPU) --------------------------
+    # Every rank holds the whole pattern; sddmm_dist_plan_coo cuts it into nnz-balanced row blocks and plans
+    # this rank's block (plus, at N > 1, the column-bucketed form used while H is being broadcast).
+    comm = None
+    if world > 1:
+        ids = [api.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)          # plumbing: 128 bytes from rank 0 to everybody
+        comm = api.Comm(handle, ids[0], rank, world)
+    else:
+        comm = api.Comm(handle, b"\0" * api.COMM_ID_BYTES, 0, 1)
+    H_CHUNKS = 8
+    dplan = comm.plan_coo(M, N, rows, cols, K, p["panel_rows"], h_chunks=H_CHUNKS)
+    plan = dplan.local
+    a, b = dplan.nnz_begin, dplan.nnz_end
+    row_begin, row_end = dplan.row_begin, dplan.row_end
+    l_rows = (rows[a:b] - row_begin).contiguous()
     l_cols = cols[a:b].contiguous()
     l_vals = vals[a:b].contiguous()
-    l_W = W[shard.row_begin:shard.row_end].contiguous() if world > 1 else W
+    l_W = W[row_begin:row_end].contiguous() if world > 1 else W
+    rows_host = rows.cpu().numpy() if (world == 1 and not args.no_cpu) else None
     h_bcast_ms = 0.0
+    bcast = None
     if world > 1:
         del W
         if rank != 0:
             H.zero_()  # only rank 0's copy counts; everyone else receives it
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
         torch.cuda.synchronize()
-        e0.record()
-        dist.broadcast(H, src=0)
-        e1.record()
-        torch.cuda.synchronize()
-        h_bcast_ms = e0.elapsed_time(e1)
-    plan = handle.plan_coo(shard.n_rows, N, l_rows, l_cols, K, p["panel_rows"], args.col_tile or p["col_tile"])
+        for _ in range(2):   # the first collective of a communicator also sets up its channels: time the second
+            dplan.execute(l_W, H, None, l_vals, root=0, flags=api.DIST_BROADCAST_ONLY)   # H arrives in H_CHUNKS pieces
+            h_bcast_ms = dplan.last_times()[0]
+            dist.barrier()
     info = plan.info()
     m_nz_local = info.n_nonempty_rows
     n_nz_local = plan.count_cols()
@@ -452,7 +461,7 @@ def main():
     kernel_name = plan.last_kernel_name()   # what actually ran: ring, ring_small, panel, gather, dense_*+...
     # ---- roofline of the dominant kernel (this rank's launch) -------------------
     peak, peak_kind = hbm_peak()
-    alg_bytes = synth.algorithmic_bytes(shard.n_rows, b - a, K, m_nz_local, n_nz_local)
+    alg_bytes = synth.algorithmic_bytes(row_end - row_begin, b - a, K, m_nz_local, n_nz_local)
     kernel_ms = statistics.mean(step_ms)
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     capture = ncu_traffic(p["workload"], kernel_name) if world == 1 else None
@@ -470,9 +479,28 @@ def main():
         roofline["dram_frac_at_capture"] = traffic / (capture["ncu_duration_ms"] * 1e-3) / 1e9 / peak
         roofline["dram_frac_estimate_live"] = traffic / (kernel_ms * 1e-3) / 1e9 / peak
         roofline["traffic_ratio"] = traffic / alg_bytes
-    gather_bytes = 4 * K * (b - a) + 4 * K * m_nz_local + 12 * (b - a) + 4 * (shard.n_rows + 1)
+    gather_bytes = 4 * K * (b - a) + 4 * K * m_nz_local + 12 * (b - a) + 4 * (row_end - row_begin + 1)
     roofline["gather_model_bytes"] = gather_bytes
     roofline["gather_model_gbs"] = gather_bytes / (kernel_ms * 1e-3) / 1e9
+
+    # ---- H broadcast overlapped with compute (N > 1): the timing protocol's t_compute + t_bcastH ----
+    if world > 1:
+        t_tot, t_bc = [], []
+        for i in range(1 + max(3, min(args.steps, 5))):
+            barrier()
+            dplan.execute(l_W, H, P, l_vals, root=0)          # chunked broadcast + bucketed kernels, synchronous
+            tb, _, tt = dplan.last_times()
+            if i > 0:
+                t_tot.append(tt)
+                t_bc.append(tb)
+        tv = torch.tensor([sum(t_tot) / len(t_tot), sum(t_bc) / len(t_bc), h_bcast_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+        bcast = {"h_bytes": 4 * N * K, "chunks": dplan.n_chunks, "t_bcast_ms": float(tv[2].item()),
+                 "t_bcast_inside_overlapped_call_ms": float(tv[1].item()), "t_compute_ms": ms_per_step,
+                 "t_compute_plus_bcast_ms": float(tv[0].item()),
+                 "overlap_ratio": float(tv[0].item()) / max(ms_per_step, float(tv[2].item())),
+                 "how": "max over ranks, CUDA events on each rank's compute stream; root's H goes out in column-range "
+                        "chunks on a communication stream, each chunk's nonzero bucket is computed as soon as it lands"}
 
     # ---- end to end through the C ABI with host buffers -------------------------
     e2e = None
@@ -490,6 +518,7 @@ def main():
             staging = {}
             up_bytes = [0]
             h_rows = multi_gpu.used_h_rows_of_slice(cols, N, rank, world) if world > 1 else None
+            phases = {} if world > 1 else None
             torch.cuda.synchronize()
 
             def e2e_step():
@@ -498,7 +527,8 @@ def main():
                 else:
                     # every rank uploads its slice of H over its own PCIe link and the slices are exchanged
                     # over NVLink while the rank's W rows and S values are uploaded; kernel; D2H P
-                    up_bytes[0] = multi_gpu.host_step(plan, rank, world, hW, hH, H, hP, hS, kflag, staging, h_rows)
+                    up_bytes[0] = multi_gpu.host_step(plan, rank, world, hW, hH, H, hP, hS, kflag, staging, h_rows,
+                                                      comm=comm, phases=phases)
 
             n_e2e = max(3, min(args.steps, 5))
             for _ in range(2):
@@ -529,6 +559,13 @@ def main():
                    "outside_the_step": "the plan (binning pass, plan_ms) and the upload of the 8 nnz bytes of row and "
                                        "column indices it keeps; the reference uploads indices inside sddmm_GPU",
                    "operand_bytes": int(tb[2].item())}
+            if phases:
+                # the last step's phases, each the max over ranks (they overlap: W/S upload runs beside the exchange)
+                ph = multi_gpu.phase_times(phases)
+                keys = sorted(ph)
+                tph = torch.tensor([ph[k] for k in keys], device=device, dtype=torch.float64)
+                dist.all_reduce(tph, op=dist.ReduceOp.MAX)
+                e2e["phases_ms_max_over_ranks"] = {k: round(float(v), 3) for k, v in zip(keys, tph.tolist())}
             # the host copy of the result is the one that is checked below
             P_check = hP
         except RuntimeError as ex:  # e.g. pinned allocation refused
@@ -579,8 +616,8 @@ def main():
         del W, H, l_W, P, hW, hH, hS, hP, P_check, results, l_rows, l_cols, l_vals
         for key in ("W", "H", "rows", "cols", "vals"):
             p.pop(key, None)
-        plan.close()
-        plan = None
+        dplan.close()
+        dplan = None
         torch.cuda.empty_cache()
         also = run_also(handle, device, peak, c4_pattern, args)
 
@@ -595,10 +632,10 @@ def main():
                        "parallelism": f"nnz-balanced row blocks x{world}", "kernel": kernel_name,
                        "panel_rows": info.panel_rows, "work_items": info.n_work_items,
                        "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms,
-                       "rank_ms_per_step": [round(x, 4) for x in rank_ms], "partition_row_cost": row_cost,
+                       "rank_ms_per_step": [round(x, 4) for x in rank_ms],
                        "dense_cells": info.n_dense_cells, "dense_cell_nnz": info.n_dense_nnz,
                        "hub_columns": info.n_hub_cols},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "parity": parity,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "parity": parity, "h_broadcast": bcast,
             # counted by the library: kernels launched by sddmm_execute / sddmm_upload_rows on this rank from the
             # first warm-up step to the end of the end-to-end steps (timed steps: one SDDMM kernel each, two when
             # the plan split S into dense cells and a remainder)

@@ -139,6 +139,27 @@ SDDMM_API int sddmm_destroy_plan(sddmm_plan_t p);
 SDDMM_API int sddmm_execute(sddmm_plan_t p, const float *W, const float *H,
                             const float *Sval, float *P, uint32_t flags);
 
+/*
+ * The step after SDDMM in its callers (the reference stops at SDDMM; its README names SDDMM "a
+ * core component in reformulations of many machine learning algorithms", README.md:1 -- there
+ * the sampled product is multiplied straight back into a dense factor).  No counterpart in the
+ * reference: parity is pinned to a CPU loop of the same definition, not to reference code.
+ *
+ *   sddmm_spmm_execute : Y[r, :] = sum over the nonzeros i of row r of Pval[i] * H[col_i, :]
+ *                        (Pval NULL: all ones).  Y is M x K, every row written (empty rows: 0).
+ *   sddmm_fused_execute: the same with Pval[i] = (sum_t W[r,t] H[col_i,t]) * Sval[i] computed on
+ *                        the fly (Sval NULL: unscaled) -- P never goes to memory and every H row
+ *                        is gathered once for both uses; P_out != NULL also stores P (input order).
+ * K a multiple of 4 up to 1024 (SDDMM_K_UNSUPPORTED otherwise).  Pointers host or device (host
+ * arrays are staged for the call); flags: 0 or SDDMM_FLAG_ASYNC (device pointers only).  Rows
+ * are processed whole by one warp, long rows in pieces that are added in a fixed order: the
+ * result does not depend on scheduling.  Works on the plan's input order (column tiles of the
+ * plan are not used).  sddmm_last_kernel_ms() reports the kernels' time.
+ */
+SDDMM_API int sddmm_spmm_execute(sddmm_plan_t p, const float *Pval, const float *H, float *Y, uint32_t flags);
+SDDMM_API int sddmm_fused_execute(sddmm_plan_t p, const float *W, const float *H, const float *Sval,
+                                  float *P_out, float *Y, uint32_t flags);
+
 /* Milliseconds of the kernels of the last synchronous sddmm_execute(), measured
  * with CUDA events on the compute stream -- the region the reference times and
  * prints as "Time for SDDMM with K = ..." (sddmm.cu:93,109-114).  For a pipelined

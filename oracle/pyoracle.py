@@ -61,6 +61,10 @@ class CpuOracle:
         L.oracle_sddmm_coo_f64.restype = None
         L.oracle_sddmm_coo_f64.argtypes = [_i32p, _i32p, C.c_void_p, C.c_int64, _f32p, _f32p, C.c_int, _f64p, _f64p, C.c_int]
         L.oracle_initial.restype = None
+        L.oracle_spmm.restype = None
+        L.oracle_spmm.argtypes = [_i32p, _i32p, C.c_void_p, C.c_int64, C.c_int64, _f32p, C.c_int, _f32p, C.c_int]
+        L.oracle_spmm_f64.restype = None
+        L.oracle_spmm_f64.argtypes = [_i32p, _i32p, C.c_void_p, C.c_int64, C.c_int64, _f32p, C.c_int, _f64p, _f64p, C.c_int]
         L.oracle_initial.argtypes = [_f32p, C.c_int64, C.c_int]
         L.oracle_make_htash.restype = None
         L.oracle_make_htash.argtypes = [_f32p, _f32p, C.c_int64, C.c_int]
@@ -109,6 +113,30 @@ class CpuOracle:
             vp = vals.ctypes.data
         self.lib.oracle_sddmm_coo_f64(rows, cols, vp, n, W, H, W.shape[1], P, A, threads)
         return P, A
+
+    def spmm(self, rows, cols, H, M, pvals=None, threads=0):
+        """Y = P H on the pattern (rows sorted): fp32, nonzeros of a row added in input order.  No counterpart in
+        the reference."""
+        rows, cols, H = _i32(rows), _i32(cols), _f32(H)
+        Y = np.empty((M, H.shape[1]), np.float32)
+        pp = None
+        if pvals is not None:
+            pvals = _f32(pvals)
+            pp = pvals.ctypes.data
+        self.lib.oracle_spmm(rows, cols, pp, rows.shape[0], M, H, H.shape[1], Y, threads)
+        return Y
+
+    def spmm_f64(self, rows, cols, H, M, pvals64=None, threads=0):
+        """float64 Y and the magnitude scale A[r, t] = sum_i |p_i H[c_i, t]| (pvals64: float64 or None)."""
+        rows, cols, H = _i32(rows), _i32(cols), _f32(H)
+        Y = np.empty((M, H.shape[1]), np.float64)
+        A = np.empty((M, H.shape[1]), np.float64)
+        pp = None
+        if pvals64 is not None:
+            pvals64 = np.ascontiguousarray(pvals64, np.float64)
+            pp = pvals64.ctypes.data
+        self.lib.oracle_spmm_f64(rows, cols, pp, rows.shape[0], M, H, H.shape[1], Y, A, threads)
+        return Y, A
 
     def initial(self, n, k):
         X = np.empty((n, k), np.float32)
@@ -229,6 +257,30 @@ class RefChecker:
         P = np.zeros(max(cols.shape[0], 1), np.float32)
         self.lib.ref_sddmm_cpu_csr(row_ptr, cols, vals, cols.shape[0], n_rows, n_cols, W, H, W.shape[1], P)
         return P[:cols.shape[0]]
+
+    def spmm(self, rows, cols, H, M, pvals=None, threads=0):
+        """Y = P H on the pattern (rows sorted): fp32, nonzeros of a row added in input order.  No counterpart in
+        the reference."""
+        rows, cols, H = _i32(rows), _i32(cols), _f32(H)
+        Y = np.empty((M, H.shape[1]), np.float32)
+        pp = None
+        if pvals is not None:
+            pvals = _f32(pvals)
+            pp = pvals.ctypes.data
+        self.lib.oracle_spmm(rows, cols, pp, rows.shape[0], M, H, H.shape[1], Y, threads)
+        return Y
+
+    def spmm_f64(self, rows, cols, H, M, pvals64=None, threads=0):
+        """float64 Y and the magnitude scale A[r, t] = sum_i |p_i H[c_i, t]| (pvals64: float64 or None)."""
+        rows, cols, H = _i32(rows), _i32(cols), _f32(H)
+        Y = np.empty((M, H.shape[1]), np.float64)
+        A = np.empty((M, H.shape[1]), np.float64)
+        pp = None
+        if pvals64 is not None:
+            pvals64 = np.ascontiguousarray(pvals64, np.float64)
+            pp = pvals64.ctypes.data
+        self.lib.oracle_spmm_f64(rows, cols, pp, rows.shape[0], M, H, H.shape[1], Y, A, threads)
+        return Y, A
 
     def initial(self, n, k):
         X = np.empty((n, k), np.float32)

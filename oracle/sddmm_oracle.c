@@ -149,6 +149,59 @@ ORACLE_API void oracle_sddmm_coo_f64(const int32_t *row_ind, const int32_t *col_
     }
 }
 
+/*
+ * SpMM on the pattern of S, the step that follows SDDMM in its callers:
+ *     Y[r, :] = sum over the nonzeros i of row r of  p_i * H[col_i, :]     (p_i = 1 when p is NULL)
+ * NO COUNTERPART IN THE REFERENCE (it stops at SDDMM), so this loop is pinned to nothing but its own
+ * definition: parity of the CUDA SpMM / fused kernels is "unpinned by the reference".  fp32, the
+ * nonzeros of a row added in input order, one rounding per multiply and per add (no FMA contraction),
+ * rows in parallel.  rows[] must be sorted.  The float64 companion also returns the magnitude
+ * scale A[r, t] = sum_i |p_i * H[col_i, t]| for the tolerance |gpu - ref| <= tol * max(|ref|, A).
+ */
+ORACLE_API void oracle_spmm(const int32_t *row_ind, const int32_t *col_ind, const float *p, int64_t nnz,
+                            int64_t n_rows, const float *H, int k, float *Y, int threads)
+{
+    if (threads < 1) threads = oracle_max_threads();
+    int64_t *row_ptr = (int64_t *)calloc((size_t)n_rows + 1, sizeof(int64_t));
+    for (int64_t i = 0; i < nnz; ++i) row_ptr[row_ind[i] + 1]++;
+    for (int64_t r = 0; r < n_rows; ++r) row_ptr[r + 1] += row_ptr[r];
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 64)
+    for (int64_t r = 0; r < n_rows; ++r) {
+        float *y = Y + r * k;
+        for (int t = 0; t < k; ++t) y[t] = 0.f;
+        for (int64_t i = row_ptr[r]; i < row_ptr[r + 1]; ++i) {
+            const float *h = H + (int64_t)col_ind[i] * k;
+            const float pi = p ? p[i] : 1.f;
+            for (int t = 0; t < k; ++t) y[t] += pi * h[t];
+        }
+    }
+    free(row_ptr);
+}
+
+ORACLE_API void oracle_spmm_f64(const int32_t *row_ind, const int32_t *col_ind, const double *p, int64_t nnz,
+                                int64_t n_rows, const float *H, int k, double *Y, double *A, int threads)
+{
+    if (threads < 1) threads = oracle_max_threads();
+    int64_t *row_ptr = (int64_t *)calloc((size_t)n_rows + 1, sizeof(int64_t));
+    for (int64_t i = 0; i < nnz; ++i) row_ptr[row_ind[i] + 1]++;
+    for (int64_t r = 0; r < n_rows; ++r) row_ptr[r + 1] += row_ptr[r];
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 64)
+    for (int64_t r = 0; r < n_rows; ++r) {
+        double *y = Y + r * k, *a = A + r * k;
+        for (int t = 0; t < k; ++t) y[t] = a[t] = 0.0;
+        for (int64_t i = row_ptr[r]; i < row_ptr[r + 1]; ++i) {
+            const float *h = H + (int64_t)col_ind[i] * k;
+            const double pi = p ? p[i] : 1.0;
+            for (int t = 0; t < k; ++t) {
+                const double v = pi * (double)h[t];
+                y[t] += v;
+                a[t] += fabs(v);
+            }
+        }
+    }
+    free(row_ptr);
+}
+
 /* HiPC18/src/util.h:68-73 (make_HTasH): H_t[t*n + r] = H[r*k + t], the K-major copy of an n x k operand. */
 ORACLE_API void oracle_make_htash(const float *H, float *H_t, int64_t n, int k)
 {

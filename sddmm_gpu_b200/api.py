@@ -34,7 +34,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_plan_coo", "sddmm_destroy_plan", "sddmm_execute", "sddmm_last_kernel_ms", "sddmm_last_transfer_bytes", "sddmm_plan_used_lines", "sddmm_upload_rows", "sddmm_coo",
     "sddmm_selftest_wait_timeout", "sddmm_plan_get_info", "sddmm_plan_count_cols", "sddmm_count_cols_noalloc", "sddmm_plan_export_row_ptr",
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
-    "sddmm_last_kernel_name", "sddmm_kernel_launches", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
+    "sddmm_spmm_execute", "sddmm_fused_execute", "sddmm_last_kernel_name", "sddmm_kernel_launches", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
     "sddmm_comm_unique_id", "sddmm_comm_create", "sddmm_comm_destroy", "sddmm_comm_broadcast", "sddmm_comm_all_gather",
     "sddmm_dist_plan_coo", "sddmm_dist_plan_destroy", "sddmm_dist_plan_get_shard", "sddmm_dist_plan_local",
     "sddmm_dist_execute", "sddmm_dist_last_times", "sddmm_multi_create", "sddmm_multi_destroy", "sddmm_multi_last_error",
@@ -87,6 +87,8 @@ def lib():
     L.sddmm_last_kernel_ms.argtypes = [vp, C.POINTER(C.c_float)]
     L.sddmm_last_kernel_name.restype = C.c_char_p
     L.sddmm_last_kernel_name.argtypes = [vp]
+    L.sddmm_spmm_execute.argtypes = [vp, vp, vp, vp, u32]
+    L.sddmm_fused_execute.argtypes = [vp, vp, vp, vp, vp, vp, u32]
     L.sddmm_sync.argtypes = [vp]
     L.sddmm_kernel_launches.argtypes = [vp, C.POINTER(i64)]
     L.sddmm_check_result.argtypes = [vp, vp, vp, vp, vp, i64, C.c_double, C.POINTER(C.c_double), C.POINTER(i64),
@@ -299,6 +301,16 @@ class Plan:
     def execute(self, W, H, P, Sval=None, flags=0):
         self.handle._follow_torch_stream(W, H, P, Sval)
         self.handle._check(lib().sddmm_execute(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P), flags))
+
+    def spmm(self, H, Y, Pval=None, flags=0):
+        """Y = P H on the plan's pattern (sddmm_spmm_execute); Pval None = all ones."""
+        self.handle._follow_torch_stream(H, Y, Pval)
+        self.handle._check(lib().sddmm_spmm_execute(self._p, _ptr(Pval), _ptr(H), _ptr(Y), flags))
+
+    def fused(self, W, H, Y, Sval=None, P_out=None, flags=0):
+        """Y = (S o (W H^T)) H without writing P (sddmm_fused_execute); P_out, if given, receives P."""
+        self.handle._follow_torch_stream(W, H, Y, Sval, P_out)
+        self.handle._check(lib().sddmm_fused_execute(self._p, _ptr(W), _ptr(H), _ptr(Sval), _ptr(P_out), _ptr(Y), flags))
 
     def last_kernel_name(self):
         return lib().sddmm_last_kernel_name(self._p).decode()

@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <atomic>
 #include <string>
+#include <vector>
 
 #include "sddmm_b200.h"
 
@@ -141,6 +142,25 @@ cudaError_t launch_dense_cells_tc(const DenseCell *cells, int64_t n_cells, const
 cudaError_t launch_ring_small(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
                               const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted,
                               int sm_count, unsigned long long *work_counter, cudaStream_t stream);
+
+// SpMM / fused SDDMM->SpMM over the plan's rows (spmm.cu).  A task is a run of whole rows
+// [row_a, row_b) (slot < 0), or the nonzeros [j0, j1) of the long row row_a, summed into scratch slot `slot`.
+struct SpmmTask {
+    int64_t j0, j1;
+    int32_t row_a, row_b;
+    int32_t slot, pad;
+};
+struct SpmmLongRow {
+    int32_t row, first_slot, n_slots;
+};
+bool spmm_supports(int K);  // K a multiple of 4, at most 1024
+// Host: tasks and long-row table from the row pointer over all M rows; *n_slots = scratch slots (K floats each).
+void build_spmm_tasks(const int64_t *row_ptr_host, int64_t M, std::vector<SpmmTask> &tasks, std::vector<SpmmLongRow> &long_rows,
+                      int64_t *n_slots);
+cudaError_t launch_spmm(bool fused, const SpmmTask *tasks, int64_t n_tasks, const SpmmLongRow *long_rows, int64_t n_long,
+                        const int64_t *row_ptr, const int32_t *cols, const float *pval, const float *W, const float *H,
+                        float *P_out, float *Y, float *scratch, int K, unsigned long long *work_counter, int sm_count,
+                        cudaStream_t stream);
 
 // float64 recomputation of every stride-th nonzero on the device (see check.cu).
 struct CheckResult {

@@ -104,6 +104,9 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_item_rows_s);
     cudaFree(p->d_used_rows);
     cudaFree(p->d_used_cols);
+    cudaFree(p->d_spmm_tasks);
+    cudaFree(p->d_spmm_long);
+    cudaFree(p->d_spmm_scratch);
     cudaFree(p->d_Wt);
     cudaFree(p->d_Ht);
     cudaFree(p->d_W);
@@ -830,6 +833,119 @@ int sddmm_check_result(sddmm_plan_t p, const float *W, const float *H, const flo
     if (n_checked) *n_checked = (int64_t)host.n_checked;
     if (n_bad) *n_bad = (int64_t)host.n_bad;
     return SDDMM_OK;
+}
+
+namespace {
+
+// Tasks of the SpMM kernels, built once per plan from the row pointer (host side: one pass over M + 1 offsets).
+int ensure_spmm_tasks(sddmm_plan_s *p)
+{
+    if (p->n_spmm_tasks >= 0) return SDDMM_OK;
+    sddmm_handle_s *h = p->h;
+    std::vector<int64_t> rp;
+    std::vector<SpmmTask> tasks;
+    std::vector<SpmmLongRow> long_rows;
+    try {
+        rp.resize((size_t)p->M + 1);
+    } catch (const std::bad_alloc &) {
+        return SDDMM_OUT_OF_MEMORY;
+    }
+    CUDA_TRY(h, cudaMemcpyAsync(rp.data(), p->d_row_ptr, sizeof(int64_t) * rp.size(), cudaMemcpyDeviceToHost, h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    int64_t slots = 0;
+    try {
+        build_spmm_tasks(rp.data(), p->M, tasks, long_rows, &slots);
+    } catch (const std::bad_alloc &) {
+        return SDDMM_OUT_OF_MEMORY;
+    }
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmm_tasks, tasks.size()));
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmm_long, long_rows.size()));
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmm_scratch, (size_t)slots * p->K));
+    if (!tasks.empty())
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_spmm_tasks, tasks.data(), sizeof(SpmmTask) * tasks.size(), cudaMemcpyHostToDevice, h->stream));
+    if (!long_rows.empty())
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_spmm_long, long_rows.data(), sizeof(SpmmLongRow) * long_rows.size(),
+                                    cudaMemcpyHostToDevice, h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    p->n_spmm_tasks = (int64_t)tasks.size();
+    p->n_spmm_long = (int64_t)long_rows.size();
+    p->n_spmm_slots = slots;
+    return SDDMM_OK;
+}
+
+// Y = P H (fused: P = S o (W H^T) on the fly).  Host arrays are staged for the call.
+int run_spmm(sddmm_plan_s *p, bool fused, const float *W, const float *H, const float *pval, float *P_out, float *Y,
+             uint32_t flags)
+{
+    sddmm_handle_s *h = p->h;
+    if (!spmm_supports(p->K)) return SDDMM_K_UNSUPPORTED;
+    if (!H || !Y || (fused && !W)) return SDDMM_INVALID_ARG;
+    if (flags & ~(uint32_t)SDDMM_FLAG_ASYNC) return SDDMM_INVALID_ARG;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    int st = ensure_spmm_tasks(p);
+    if (st != SDDMM_OK) return st;
+    cudaStream_t s = h->stream;
+    struct Tmp {
+        void *p[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        ~Tmp() { for (void *q : p) if (q) cudaFree(q); }
+    } tmp;
+    auto stage_in = [&](int slot, const float *src, size_t count, const float **dst) -> cudaError_t {
+        if (!src || is_device_ptr(src)) { *dst = src; return cudaSuccess; }
+        cudaError_t e = cudaMalloc(&tmp.p[slot], sizeof(float) * (count ? count : 1));
+        if (e != cudaSuccess) return e;
+        *dst = (const float *)tmp.p[slot];
+        return cudaMemcpyAsync(tmp.p[slot], src, sizeof(float) * count, cudaMemcpyHostToDevice, s);
+    };
+    const size_t mk = (size_t)p->M * p->K, nk = (size_t)p->N * p->K, nz = (size_t)p->nnz;
+    const float *dW = nullptr, *dH = nullptr, *dV = nullptr;
+    CUDA_TRY(h, stage_in(0, W, mk, &dW));
+    CUDA_TRY(h, stage_in(1, H, nk, &dH));
+    CUDA_TRY(h, stage_in(2, pval, nz, &dV));
+    float *dY = Y, *dP = P_out;
+    const bool y_dev = is_device_ptr(Y), p_dev = P_out ? is_device_ptr(P_out) : true;
+    if ((flags & SDDMM_FLAG_ASYNC) && (!y_dev || !p_dev || tmp.p[0] || tmp.p[1] || tmp.p[2])) return SDDMM_INVALID_ARG;
+    if (!y_dev) {
+        CUDA_TRY(h, cudaMalloc(&tmp.p[3], sizeof(float) * (mk ? mk : 1)));
+        dY = (float *)tmp.p[3];
+    }
+    if (P_out && !p_dev) {
+        CUDA_TRY(h, cudaMalloc(&tmp.p[4], sizeof(float) * (nz ? nz : 1)));
+        dP = (float *)tmp.p[4];
+    }
+    if ((((uintptr_t)dW | (uintptr_t)dH | (uintptr_t)dY) & 15u) != 0) {
+        h->last_error = "W, H and Y must be 16-byte aligned on the device";
+        return SDDMM_INVALID_ARG;
+    }
+    CUDA_TRY(h, cudaEventRecord(h->ev0, s));
+    if (p->M > 0)
+        LAUNCH_TRY(h, launch_spmm(fused, p->d_spmm_tasks, p->n_spmm_tasks, p->d_spmm_long, p->n_spmm_long, p->d_row_ptr, p->d_cols,
+                                  dV, dW, dH, dP, dY, p->d_spmm_scratch, p->K, h->d_work_counter, h->sm_count, s));
+    CUDA_TRY(h, cudaEventRecord(h->ev1, s));
+    p->last_kernel = fused ? "fused_sddmm_spmm" : "spmm";
+    if (!y_dev) CUDA_TRY(h, cudaMemcpyAsync(Y, dY, sizeof(float) * mk, cudaMemcpyDeviceToHost, s));
+    if (P_out && !p_dev) CUDA_TRY(h, cudaMemcpyAsync(P_out, dP, sizeof(float) * nz, cudaMemcpyDeviceToHost, s));
+    if (flags & SDDMM_FLAG_ASYNC) {
+        p->last_ms = -1.f;
+        return SDDMM_OK;
+    }
+    CUDA_TRY(h, cudaStreamSynchronize(s));
+    CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
+    return SDDMM_OK;
+}
+
+}  // namespace
+
+int sddmm_spmm_execute(sddmm_plan_t p, const float *Pval, const float *H, float *Y, uint32_t flags)
+{
+    if (!p) return SDDMM_INVALID_ARG;
+    return run_spmm(p, false, nullptr, H, Pval, nullptr, Y, flags);
+}
+
+int sddmm_fused_execute(sddmm_plan_t p, const float *W, const float *H, const float *Sval, float *P_out, float *Y,
+                        uint32_t flags)
+{
+    if (!p) return SDDMM_INVALID_ARG;
+    return run_spmm(p, true, W, H, Sval, P_out, Y, flags);
 }
 
 int sddmm_selftest_optin_cache(void)

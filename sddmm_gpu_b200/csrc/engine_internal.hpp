@@ -86,5 +86,10 @@ struct sddmm_plan_s {
     int64_t n_used_rows = 0, n_used_cols = 0;
     int64_t last_h2d_bytes = 0, last_d2h_bytes = 0;  // moved by the last sddmm_execute
     const char *last_kernel = "none";                // kernels the last sddmm_execute launched
+    // SpMM / fused SDDMM->SpMM over the plan's rows (built on first use): tasks, long-row table, scratch
+    SpmmTask *d_spmm_tasks = nullptr;
+    SpmmLongRow *d_spmm_long = nullptr;
+    float *d_spmm_scratch = nullptr;
+    int64_t n_spmm_tasks = -1, n_spmm_long = 0, n_spmm_slots = 0;
 };
 

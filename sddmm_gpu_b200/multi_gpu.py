@@ -124,7 +124,7 @@ def used_h_rows_of_slice(cols_all, N, rank, world):
 
 
 def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=None, flags=0, staging=None,
-              h_slice_rows=None):
+              h_slice_rows=None, comm=None, phases=None):
     """One SDDMM on this rank's row block with every operand in (pinned) host memory:
     this rank's rows of W, its 1/world slice of H's rows, its S values; P comes back to
     host memory.  Order on the rank's PCIe link: the H slice first, then W rows and S
@@ -133,20 +133,32 @@ def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=
     when both are in place.  Only rows that a nonzero touches travel over PCIe: the rows
     of W from the plan's own list, the rows of the H slice from `h_slice_rows`
     (used_h_rows_of_slice; None uploads the whole slice).  `staging` (a dict the caller
-    keeps) holds the device copies of W and S and the side stream between calls."""
+    keeps) holds the device copies of W and S and the side stream between calls.
+    `comm` (an api.Comm) exchanges the H slices through the C ABI's all-gather instead of torch.distributed
+    when the slices have equal length.  `phases` (a dict) receives CUDA events around the phases of the step;
+    phase_times() turns them into milliseconds after the step has completed."""
     staging = staging if staging is not None else {}
     handle, K = plan.handle, H_dev.shape[1]
     cur = torch.cuda.current_stream()
     side = staging.get("side")
     if side is None:
         side = staging["side"] = torch.cuda.Stream()
+    def mark(name, stream):
+        if phases is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            phases[name] = ev
+
+    mark("begin", cur)
     a, b = h_slice_bounds(H_dev.shape[0], rank, world)
     if h_slice_rows is not None:
         handle.upload_rows(H_host_slice, H_dev[a:b], h_slice_rows, h_slice_rows.numel(), K, cur.cuda_stream)
     else:
         H_dev[a:b].copy_(H_host_slice, non_blocking=True)
-    slice_up = torch.cuda.Event()
+    slice_up = torch.cuda.Event(enable_timing=phases is not None)
     slice_up.record(cur)
+    if phases is not None:
+        phases["h_slice_uploaded"] = slice_up
 
     def staged(name, host):
         t = staging.get(name)
@@ -163,11 +175,34 @@ def host_step(plan, rank, world, W_host, H_host_slice, H_dev, P_host, Sval_host=
         if Sval_host is not None:
             S_dev = staged("S", Sval_host)
             S_dev.copy_(Sval_host, non_blocking=True)
-    exchange_h_slices(H_dev, rank, world)
+        mark("w_uploaded", side)
+    n = H_dev.shape[0]
+    if comm is not None and world > 1 and n % world == 0:
+        comm.all_gather(H_dev, (n // world) * K, cur.cuda_stream)
+    else:
+        exchange_h_slices(H_dev, rank, world)
+    mark("h_exchanged", cur)
     cur.wait_stream(side)
     plan.execute(W_dev, H_dev, P_host, S_dev, flags)   # kernel and download of P; synchronous
+    mark("end", cur)
+    if phases is not None:
+        phases["kernel_ms"] = plan.last_kernel_ms()
     n_h = h_slice_rows.numel() if h_slice_rows is not None else (b - a)
     return 4 * K * (n_ids + n_h) + (4 * Sval_host.numel() if Sval_host is not None else 0)   # bytes uploaded
+
+
+def phase_times(phases):
+    """Milliseconds of the phases of one host_step (after it has completed), on this rank: the upload of
+    the rank's H slice, the exchange of the slices, the upload of W and S (runs beside the exchange, on the
+    side stream, from the moment the H slice is up), the kernel, and what is left of the step after the
+    later of exchange and W upload (kernel + download of P)."""
+    b, e = phases["begin"], phases["end"]
+    up, ex, w = phases["h_slice_uploaded"], phases["h_exchanged"], phases["w_uploaded"]
+    total = b.elapsed_time(e)
+    t_ex, t_w = b.elapsed_time(ex), b.elapsed_time(w)
+    return {"h_slice_upload_ms": b.elapsed_time(up), "h_exchange_ms": up.elapsed_time(ex),
+            "w_s_upload_ms": up.elapsed_time(w), "kernel_ms": phases["kernel_ms"],
+            "p_download_and_sync_ms": total - max(t_ex, t_w) - phases["kernel_ms"], "total_ms": total}
 
 
 class ShardedSddmm:

@@ -108,7 +108,7 @@ plan.execute(dW, dH, P, dS, flags=api.DIST_H_RESIDENT)
 assert_parity(P.cpu().numpy(), lr, cols[a:b], W[plan.row_begin:plan.row_end], H, vals[a:b])
 plan.close(); comm.close(); h.close()
 dist.barrier(); dist.destroy_process_group()
-print("rank", rank, "ok")
+open(os.path.join(sys.argv[2], f"rank{rank}.ok"), "w").write("ok")
 """
 
 
@@ -121,7 +121,7 @@ def test_one_process_per_gpu_overlapped_broadcast(tmp_path):
     script.write_text(_RANK_SCRIPT)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29533", str(script), ROOT],
+                          "--master-addr", "127.0.0.1", "--master-port", "29533", str(script), ROOT, str(tmp_path)],
                          capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
+    assert (tmp_path / "rank0.ok").exists() and (tmp_path / "rank1.ok").exists()

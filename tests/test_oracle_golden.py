@@ -128,3 +128,28 @@ def test_fp32_reference_itself_misses_1e4_between_1e3_and_1e2():
     assert rel[band].max() > 1e-4 / 2          # the reference's own rounding uses up the tolerance in the band ...
     assert rel[well].max() < 1e-4 / 2          # ... and stays well inside it on the well-conditioned nonzeros
     assert np.all(np.abs(P32 - P64) <= 1e-5 * A)   # while the magnitude-scaled error is tiny everywhere
+
+
+def test_spmm_oracle_against_numpy():
+    """oracle_spmm / oracle_spmm_f64 (no counterpart in the reference) against a plain numpy restatement:
+    integer-valued operands make every sum exact, so the comparison is bit for bit."""
+    rng = np.random.default_rng(2)
+    M, N, K, nnz = 37, 23, 12, 200
+    rows = np.sort(rng.integers(0, M, nnz)).astype(np.int32)
+    cols = rng.integers(0, N, nnz).astype(np.int32)
+    p = rng.integers(-3, 4, nnz).astype(np.float32)
+    H = rng.integers(-4, 5, (N, K)).astype(np.float32)
+    want = np.zeros((M, K), np.float64)
+    mag = np.zeros((M, K), np.float64)
+    for r, c, v in zip(rows, cols, p):
+        want[r] += float(v) * H[c].astype(np.float64)
+        mag[r] += np.abs(float(v) * H[c].astype(np.float64))
+    assert np.array_equal(oracle.cpu.spmm(rows, cols, H, M, p), want.astype(np.float32))
+    assert np.array_equal(oracle.cpu.spmm(rows, cols, H, M, p, threads=1), want.astype(np.float32))
+    Y64, A = oracle.cpu.spmm_f64(rows, cols, H, M, p.astype(np.float64))
+    assert np.array_equal(Y64, want) and np.array_equal(A, mag)
+    ones = oracle.cpu.spmm(rows, cols, H, M)                      # bare pattern
+    want1 = np.zeros((M, K), np.float64)
+    for r, c in zip(rows, cols):
+        want1[r] += H[c]
+    assert np.array_equal(ones, want1.astype(np.float32))
