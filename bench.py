@@ -52,7 +52,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "cusparse"],
+                    help="ours; the reference's CPU SDDMM; or cuSPARSE's SDDMM as a labelled library comparator")
     ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c5", "c5b"])
     ap.add_argument("--k", type=int, default=0, help="override K of the workload")
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (c3/c4), for quick runs")
@@ -246,6 +247,50 @@ def quick_run(handle, p, peak, steps=5, warmup=3):
     return out
 
 
+def quick_run_fused(handle, p, peak, steps=5, warmup=3):
+    """The fused SDDMM->SpMM (Y = (S o (W H^T)) H, P never stored) and the unfused pair (SDDMM, then SpMM over the
+    stored P) on one configuration; algorithmic bytes of the fused form: every touched row of W and H once, Y
+    written once (all M rows), per nonzero a column index and an S value, the row pointer."""
+    from sddmm_gpu_b200 import api
+    nnz, M, K = int(p["rows"].shape[0]), p["M"], p["K"]
+    plan = handle.plan_coo(M, p["N"], p["rows"], p["cols"], K)
+    info = plan.info()
+    dev = p["rows"].device
+    Y = torch.empty((M, K), device=dev, dtype=torch.float32)
+    P = torch.empty(nnz, device=dev, dtype=torch.float32)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record()
+        for i in range(steps):
+            fn()
+            evs[i + 1].record()
+        handle.sync()
+        return sum(evs[i].elapsed_time(evs[i + 1]) for i in range(steps)) / steps
+
+    t_fused = timed(lambda: plan.fused(p["W"], p["H"], Y, p["vals"], None, api.FLAG_ASYNC))
+    Yf = Y.clone()
+
+    def pair():
+        plan.execute(p["W"], p["H"], P, p["vals"], api.FLAG_ASYNC)
+        plan.spmm(p["H"], Y, P, api.FLAG_ASYNC)
+
+    t_pair = timed(pair)
+    # the two routes agree up to the rounding of P (the fused form is checked against the CPU loops in the tests)
+    scale = float(Y.abs().max()) + 1e-30
+    diff = float((Y - Yf).abs().max()) / scale
+    n_nz = plan.count_cols()
+    alg = 4 * K * (info.n_nonempty_rows + n_nz) + 4 * K * M + 8 * nnz + 8 * (M + 1)
+    out = {"workload": p["workload"], "op": "fused_sddmm_spmm", "nnz": nnz, "K": K, "ms_per_step": t_fused,
+           "unfused_pair_ms": t_pair, "gflops": 4.0 * nnz * K / (t_fused * 1e-3) / 1e9, "algorithmic_bytes": alg,
+           "frac": alg / (t_fused * 1e-3) / 1e9 / peak, "kernel": "fused_sddmm_spmm",
+           "max_diff_vs_unfused_pair_rel_to_max": diff, "steps": steps}
+    plan.close()
+    return out
+
+
 def run_also(handle, device, peak, c4_pattern, args):
     """The other benchmark configurations and the ends of config 4's K sweep, a few steps each, so that
     one default run shows every configuration's time and roofline fraction (frac = algorithmic bytes /
@@ -253,10 +298,18 @@ def run_also(handle, device, peak, c4_pattern, args):
     from sddmm_gpu_b200 import synth
     out = []
 
-    def go(make):
+    def go(make, compare=False):
         p = make()
         try:
             out.append(quick_run(handle, p, peak))
+            if compare:
+                # same operands through cuSPARSE's SDDMM: a library comparator beside this entry's time
+                try:
+                    ms, _ = cusparse_sddmm_ms(p)
+                    out[-1]["comparators"] = {"cusparse_ms": ms, "what": "cusparseSDDMM via torch.sparse.sampled_addmm, "
+                                                                        "CSR fp32, then values * S"}
+                except Exception as ex:
+                    out[-1]["comparators"] = {"cusparse_ms": None, "error": str(ex)[:160]}
         except Exception as ex:  # a failure here must not lose the headline line
             out.append({"workload": p.get("workload", "?"), "error": str(ex)[:200]})
         del p
@@ -276,9 +329,26 @@ def run_also(handle, device, peak, c4_pattern, args):
                             W=torch.randn((M, K), generator=g, device=device) * 0.1,
                             H=torch.randn((N, K), generator=g, device=device) * 0.1, panel_rows=192, col_tile=1 << 30)
             go(make)
+    if c4_pattern is not None:
+        rows, cols, vals, M, N = c4_pattern
+
+        def make_fused():
+            g = torch.Generator(device=device)
+            g.manual_seed(synth.SEEDS["c4"] + 256)
+            return dict(M=M, N=N, K=256, rows=rows, cols=cols, vals=vals, workload="c4_rmat_scale22_ef24_K256",
+                        W=torch.randn((M, 256), generator=g, device=device) * 0.1,
+                        H=torch.randn((N, 256), generator=g, device=device) * 0.1)
+        go(make_fused, compare=True)            # config 4 at K = 256 once more, beside cuSPARSE on the same operands
+        pf = make_fused()
+        try:
+            out.append(quick_run_fused(handle, pf, peak))
+        except Exception as ex:
+            out.append({"workload": pf["workload"], "op": "fused_sddmm_spmm", "error": str(ex)[:200]})
+        del pf
+        torch.cuda.empty_cache()
     go(lambda: named(synth.uniform_sparse(device=device), "c1_uniform_4096x4096_d0.001"))
-    go(lambda: named(synth.bag_of_words(device=device), "c2_bagofwords_12419x1500_nnz746316"))
-    go(lambda: named(synth.rmat(device=device), "c3_rmat_scale20_ef16"))
+    go(lambda: named(synth.bag_of_words(device=device), "c2_bagofwords_12419x1500_nnz746316"), compare=True)
+    go(lambda: named(synth.rmat(device=device), "c3_rmat_scale20_ef16"), compare=True)
     go(lambda: named(synth.attention_mask(device=device), "c5_attention_65536_band256_g80"))
     go(lambda: named(synth.attention_mask(n_global=1311, device=device), "c5b_attention_65536_band256_g1311"))
     return out
@@ -353,6 +423,82 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def cusparse_sddmm_ms(p, steps=3, warmup=2):
+    """Milliseconds per SDDMM of cuSPARSE's kernel (torch.sparse.sampled_addmm on the CSR pattern, then * S) on the
+    operands of problem p: a labelled library comparator, nothing of this repository runs in it."""
+    device = p["rows"].device
+    M, N, nnz = p["M"], p["N"], int(p["rows"].shape[0])
+    crow = torch.zeros(M + 1, dtype=torch.int64, device=device)
+    crow[1:] = torch.cumsum(torch.bincount(p["rows"], minlength=M), 0)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        pattern = torch.sparse_csr_tensor(crow.to(torch.int32), p["cols"], torch.zeros(nnz, device=device), size=(M, N))
+    Ht = p["H"].t()
+
+    def step():
+        return torch.sparse.sampled_addmm(pattern, p["W"], Ht, beta=0.0, alpha=1.0).values() * p["vals"]
+
+    for _ in range(warmup):
+        res = step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        res = step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, res
+
+
+def run_cusparse(args, rank):
+    """--impl cusparse: cuSPARSE's SDDMM (through torch.sparse.sampled_addmm on a CSR pattern) on the same
+    synthetic operands, one GPU, rank 0.  A labelled LIBRARY comparator: it says how a vendor kernel does on
+    the workload; it is neither the product nor the oracle."""
+    if rank != 0:
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "cusparse", "unavailable": "no CUDA device"}), flush=True)
+        return
+    device = torch.device("cuda", 0)
+    p = make_problem(args, device)
+    M, N, K = p["M"], p["N"], p["K"]
+    rows, cols, vals, W, H = p["rows"], p["cols"], p["vals"], p["W"], p["H"]
+    nnz = int(rows.shape[0])
+    try:
+        crow = torch.zeros(M + 1, dtype=torch.int64, device=device)
+        crow[1:] = torch.cumsum(torch.bincount(rows, minlength=M), 0)
+        # cuSPARSE's SDDMM computes alpha (A B) o spy(C) + beta C: the pattern only; S's values are applied afterwards
+        pattern = torch.sparse_csr_tensor(crow.to(torch.int32), cols, torch.zeros(nnz, device=device), size=(M, N))
+        Ht = H.t()   # a view: op(B) = H^T, no copy of H
+        steps, warmup = args.steps, max(args.warmup, 3)
+
+        def step():
+            out = torch.sparse.sampled_addmm(pattern, W, Ht, beta=0.0, alpha=1.0)
+            return out.values() * vals
+
+        for _ in range(warmup):
+            res = step()
+        torch.cuda.synchronize()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record()
+        for i in range(steps):
+            res = step()
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        ms = sum(evs[i].elapsed_time(evs[i + 1]) for i in range(steps)) / steps
+        worst, n_checked = oracle_sample_check(rows, cols, vals, W, H, [res], 65_536, 64)
+        line = {"impl": "cusparse", "metric": "SDDMM GFLOP/s (2*nnz*K)", "value": 2.0 * nnz * K / (ms * 1e-3) / 1e9,
+                "unit": "GFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+                "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": p["workload"], "M": M, "N": N, "nnz": nnz, "K": K},
+                "library": "cusparseSDDMM via torch.sparse.sampled_addmm (CSR, fp32), then values * S",
+                "parity_max_scaled_err": worst, "parity_n_checked": n_checked}
+    except Exception as ex:
+        line = {"impl": "cusparse", "unavailable": str(ex)[:300]}
+    print(json.dumps(line), flush=True)
+
+
 def p_workload(args):
     K = args.k or {"c1": 32, "c2": 256, "c3": 128, "c4": 256, "c5": 64, "c5b": 64}[args.workload]
     s3, s4 = args.scale or 20, args.scale or 22
@@ -368,6 +514,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.impl == "cusparse":
+        run_cusparse(args, rank)
         return
 
     if not torch.cuda.is_available():
