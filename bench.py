@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (c3/c4), for quick runs")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "panel", "gather"])
     ap.add_argument("--col-tile", type=int, default=0, help="column-tile width passed to the plan (argv[4] of the CLI)")
+    ap.add_argument("--op", default="sddmm", choices=["sddmm", "sddmm_bf16", "fused"],
+                    help="sddmm: the benchmark proper.  sddmm_bf16 / fused: a short device-resident timing of the opt-in "
+                         "bfloat16-operand SDDMM or of the fused SDDMM->SpMM on the chosen workload (one GPU), one JSON line")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
@@ -218,31 +221,42 @@ def oracle_sample_check(rows_d, cols_d, vals_d, W_d, H_d, results, n_sample=262_
     return worst, int(idx.shape[0])
 
 
-def quick_run(handle, p, peak, steps=5, warmup=3):
+def quick_run(handle, p, peak, steps=5, warmup=3, bf16=False):
     """A short device-resident timing of one configuration: plan, warm-up, `steps` timed executes
-    (CUDA events on the launching stream), a sampled oracle check."""
+    (CUDA events on the launching stream), a sampled oracle check.  bf16: the opt-in bfloat16 operand
+    storage (fp32 accumulate), checked against the oracle on the rounded operands."""
     from sddmm_gpu_b200 import api, synth
     nnz = int(p["rows"].shape[0])
+    if bf16:
+        p = dict(p)
+        p["W16"], p["H16"] = p["W"].to(torch.bfloat16), p["H"].to(torch.bfloat16)
+        p["W"], p["H"] = p["W16"].float(), p["H16"].float()     # what the kernel sees, for the oracle
+    Wk, Hk = (p["W16"], p["H16"]) if bf16 else (p["W"], p["H"])
+    xflag = api.FLAG_OPERANDS_BF16 if bf16 else 0
     plan = handle.plan_coo(p["M"], p["N"], p["rows"], p["cols"], p["K"], p.get("panel_rows", 0), p.get("col_tile", 0))
     info = plan.info()
     P = torch.empty(nnz, device=p["rows"].device, dtype=torch.float32)
     for _ in range(warmup):
-        plan.execute(p["W"], p["H"], P, p["vals"], api.FLAG_ASYNC)
+        plan.execute(Wk, Hk, P, p["vals"], api.FLAG_ASYNC | xflag)
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     evs[0].record()
     for i in range(steps):
-        plan.execute(p["W"], p["H"], P, p["vals"], api.FLAG_ASYNC)
+        plan.execute(Wk, Hk, P, p["vals"], api.FLAG_ASYNC | xflag)
         evs[i + 1].record()
     handle.sync()
     ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
     mean_ms = sum(ms) / len(ms)
     alg = synth.algorithmic_bytes(p["M"], nnz, p["K"], info.n_nonempty_rows, plan.count_cols())
+    if bf16:   # operand rows are half as long
+        alg -= 2 * p["K"] * (info.n_nonempty_rows + plan.count_cols())
     worst, n_checked = oracle_sample_check(p["rows"], p["cols"], p["vals"], p["W"], p["H"], [P], 65_536, 64)
     out = {"workload": p["workload"], "nnz": nnz, "K": p["K"], "ms_per_step": mean_ms, "ms_min": min(ms),
            "gflops": 2.0 * nnz * p["K"] / (mean_ms * 1e-3) / 1e9, "algorithmic_bytes": alg,
            "frac": alg / (mean_ms * 1e-3) / 1e9 / peak, "kernel": plan.last_kernel_name(),
            "dense_cell_share": (info.n_dense_nnz / nnz) if nnz else 0.0, "plan_ms": info.plan_ms,
            "parity_max_scaled_err": worst, "parity_n_checked": n_checked, "steps": steps}
+    if bf16:
+        out["operands"] = "bf16 storage, fp32 accumulate (opt-in, outside the fp32 tolerance contract; oracle on rounded operands)"
     plan.close()
     return out
 
@@ -298,10 +312,10 @@ def run_also(handle, device, peak, c4_pattern, args):
     from sddmm_gpu_b200 import synth
     out = []
 
-    def go(make, compare=False):
+    def go(make, compare=False, bf16=False):
         p = make()
         try:
-            out.append(quick_run(handle, p, peak))
+            out.append(quick_run(handle, p, peak, bf16=bf16))
             if compare:
                 # same operands through cuSPARSE's SDDMM: a library comparator beside this entry's time
                 try:
@@ -339,6 +353,7 @@ def run_also(handle, device, peak, c4_pattern, args):
                         W=torch.randn((M, 256), generator=g, device=device) * 0.1,
                         H=torch.randn((N, 256), generator=g, device=device) * 0.1)
         go(make_fused, compare=True)            # config 4 at K = 256 once more, beside cuSPARSE on the same operands
+        go(make_fused, bf16=True)               # and with the operands stored in bfloat16
         pf = make_fused()
         try:
             out.append(quick_run_fused(handle, pf, peak))
@@ -532,6 +547,17 @@ def main():
     rows, cols, vals, W, H = p["rows"], p["cols"], p["vals"], p["W"], p["H"]
     nnz = int(rows.shape[0])
     handle = api.Handle(local_rank)
+    if args.op != "sddmm":
+        # the neighbouring operations: not the headline metric, one short timing each
+        if world > 1:
+            raise SystemExit("--op sddmm_bf16 / fused run on one GPU")
+        peak, _ = hbm_peak()
+        steps = max(args.steps, 3)
+        out = quick_run_fused(handle, p, peak, steps) if args.op == "fused" else quick_run(handle, p, peak, steps, bf16=True)
+        out.update({"op": args.op, "unit": "GFLOP/s", "value": out["gflops"], "n_gpus": 1, "data": "synthetic"})
+        print(json.dumps(out), flush=True)
+        handle.close()
+        return
     # Everything below runs on one explicit (non-default) torch stream that the
     # engine is told to launch on, so that torch's CUDA events see its kernels.
     stream = torch.cuda.Stream(device=device)

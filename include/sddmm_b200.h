@@ -55,6 +55,12 @@ enum {
 #define SDDMM_FLAG_KERNEL_PANEL  0x20u /* force the TMA-staged row-panel kernel */
 #define SDDMM_FLAG_KERNEL_RING   0x40u /* force the shared-memory gather-ring kernels (K = 32, 64, 128, 256, 512 or 1024) */
 
+#define SDDMM_FLAG_OPERANDS_BF16 0x100u /* W and H point to bfloat16 arrays (row-major, 2 bytes per element; K = 256, 512,
+                                          1024 or 2048); products and sums stay fp32.  Opt-in, outside the fp32 tolerance
+                                          contract (operands carry 8 bits of mantissa); halves the bytes of every gather.
+                                          Device arrays only; no counterpart in the reference, whose operands are fp32
+                                          (HiPC18/src/sddmm.cu:32) */
+
 /* ---- plan flags ---------------------------------------------------------- */
 #define SDDMM_PLAN_SKIP_VALIDATION 0x1u /* trust sortedness and bounds (the reference checks neither) */
 #define SDDMM_PLAN_DEVICE_INDICES  0x2u /* rows/cols are device pointers on the handle's device */

@@ -25,6 +25,7 @@ FLAG_W_TRANSPOSED = 0x8
 FLAG_KERNEL_GATHER = 0x10
 FLAG_KERNEL_PANEL = 0x20
 FLAG_KERNEL_RING = 0x40
+FLAG_OPERANDS_BF16 = 0x100
 PLAN_SKIP_VALIDATION = 0x1
 PLAN_DEVICE_INDICES = 0x2
 PLAN_FORCE_H_CHUNKS = 0x4

@@ -119,6 +119,13 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
                         const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
 
+// The same TMA rings over operands stored in bfloat16 (rows of 2K bytes; products and sums in fp32):
+// K = 256, 512, 1024 or 2048.  Opt-in, outside the fp32 tolerance contract.
+bool ring_bf16_supports(int K);
+cudaError_t launch_ring_bf16(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
+                             const void *W_bf16, const void *H_bf16, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
+                             unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
+
 // Dense-cell kernel: every dense cell is computed as the 128 x 64 block
 // W[rows] * H[cols]^T -- fp32 FMAs, or (tensor) 3xTF32 on the tensor cores -- then
 // the cell's nonzeros pick their entries: P[idx[i]] = block[rc[i]] (* sval[idx[i]]).

@@ -478,6 +478,36 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
     const bool all_dev = w_dev && h_dev && p_dev && s_dev;
     if ((flags & SDDMM_FLAG_ASYNC) && !all_dev) return SDDMM_INVALID_ARG;
 
+    if (flags & SDDMM_FLAG_OPERANDS_BF16) {
+        // W and H hold bfloat16: the TMA rings over rows of 2K bytes, products and sums in fp32.  Opt-in and
+        // outside the fp32 tolerance contract; device arrays only, no other layout or kernel flag.
+        if (!ring_bf16_supports(p->K)) return SDDMM_K_UNSUPPORTED;
+        if (!all_dev || (flags & ~(uint32_t)(SDDMM_FLAG_OPERANDS_BF16 | SDDMM_FLAG_ASYNC | SDDMM_FLAG_KERNEL_RING))) {
+            h->last_error = "SDDMM_FLAG_OPERANDS_BF16 takes device arrays and no flag but ASYNC / KERNEL_RING";
+            return SDDMM_INVALID_ARG;
+        }
+        if ((((uintptr_t)W | (uintptr_t)H) & 15u) != 0) {
+            h->last_error = "W and H must be 16-byte aligned on the device";
+            return SDDMM_INVALID_ARG;
+        }
+        const bool tiled = p->d_perm != nullptr;
+        const int32_t *rows_p = tiled ? p->d_rows_t : p->d_rows;
+        const int32_t *cols_p = p->d_cols_hint ? p->d_cols_hint : (tiled ? p->d_cols_t : p->d_cols);
+        p->last_kernel = "ring (bf16 operands)";
+        p->last_h2d_bytes = p->last_d2h_bytes = 0;
+        CUDA_TRY(h, cudaEventRecord(h->ev0, s));
+        LAUNCH_TRY(h, launch_ring_bf16(rows_p, cols_p, tiled ? p->d_perm : nullptr, Sval, W, H, P, p->nnz, p->K,
+                                       p->d_cols_hint != nullptr, h->sm_count, h->d_work_counter, h->d_status, s));
+        CUDA_TRY(h, cudaEventRecord(h->ev1, s));
+        if (flags & SDDMM_FLAG_ASYNC) {
+            p->last_ms = -1.f;
+            return SDDMM_OK;
+        }
+        CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(h, cudaStreamSynchronize(s));
+        CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
+        return check_device_status(h);
+    }
     const float *dW = W, *dH = H, *dS = Sval;
     float *dP = P;
     const size_t wbytes = sizeof(float) * (size_t)p->M * p->K, hbytes = sizeof(float) * (size_t)p->N * p->K;

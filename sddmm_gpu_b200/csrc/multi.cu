@@ -672,20 +672,23 @@ int sddmm_multi_execute(sddmm_multi_plan_t p, const float *W, const float *H, co
         CU_TRY(h, cudaSetDevice(h->device));
         cudaStream_t s = h->stream;
         const int64_t lm = d->row_end - d->row_begin, ln = d->nnz_end - d->nnz_begin;
-        // this GPU's slice of H first (the exchange waits for it), then its rows of W and its S values
+        // All uploads first, the exchange after them: a copy from pageable host memory blocks its host thread
+        // until the stream has caught up, and a thread that sits in such a call while its GPU's all-gather waits
+        // for peers whose threads have not launched theirs yet is the classic way to stall every GPU of a
+        // one-process job.  With the copies in front, no thread blocks between the collective's launches.
         const int64_t h0 = std::min<int64_t>(p->N, slice * r), h1 = std::min<int64_t>(p->N, slice * (r + 1));
         if (h1 > h0)
             CU_TRY(h, cudaMemcpyAsync(p->dH[(size_t)r] + (size_t)h0 * K, H + (size_t)h0 * K, sizeof(float) * (size_t)(h1 - h0) * K,
                                       cudaMemcpyHostToDevice, s));
-        if (n > 1) {
-            const int cst = sddmm_comm_all_gather(m->comms[(size_t)r], p->dH[(size_t)r], slice * K, s);
-            if (cst != SDDMM_OK) return cst;
-        }
         if (lm > 0)
             CU_TRY(h, cudaMemcpyAsync(p->dW[(size_t)r], W + (size_t)d->row_begin * K, sizeof(float) * (size_t)lm * K,
                                       cudaMemcpyHostToDevice, s));
         if (Sval && ln > 0)
             CU_TRY(h, cudaMemcpyAsync(p->dS[(size_t)r], Sval + d->nnz_begin, sizeof(float) * (size_t)ln, cudaMemcpyHostToDevice, s));
+        if (n > 1) {
+            const int cst = sddmm_comm_all_gather(m->comms[(size_t)r], p->dH[(size_t)r], slice * K, s);
+            if (cst != SDDMM_OK) return cst;
+        }
         if (ln > 0) {
             const int est = sddmm_dist_execute(d, p->dW[(size_t)r], p->dH[(size_t)r], Sval ? p->dS[(size_t)r] : nullptr,
                                                p->dP[(size_t)r], 0, flags | SDDMM_DIST_H_RESIDENT);

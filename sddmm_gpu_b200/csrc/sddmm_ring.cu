@@ -76,6 +76,31 @@ struct RingShape {
     static_assert(B >= 1 && B <= 8 && LPN * B == 32, "group geometry");
 };
 
+// A 16-byte piece of a row: four fp32 values, or eight bfloat16 values (operand storage
+// in bfloat16, products and sums in fp32: a bfloat16 is the upper half of an fp32, so
+// widening is a shift or a mask).
+template <bool BF16>
+struct Piece {
+    using T = float4;
+    static __device__ __forceinline__ float dot(T a, T b, float acc) { return dot4(a, b, acc); }
+};
+template <>
+struct Piece<true> {
+    using T = uint4;
+    static __device__ __forceinline__ float dot2(unsigned a, unsigned b, float acc)
+    {
+        acc = fmaf(__uint_as_float(a << 16), __uint_as_float(b << 16), acc);
+        return fmaf(__uint_as_float(a & 0xffff0000u), __uint_as_float(b & 0xffff0000u), acc);
+    }
+    static __device__ __forceinline__ float dot(T a, T b, float acc)
+    {
+        acc = dot2(a.x, b.x, acc);
+        acc = dot2(a.y, b.y, acc);
+        acc = dot2(a.z, b.z, acc);
+        return dot2(a.w, b.w, acc);
+    }
+};
+
 // The column indices a lane needs to issue a group: its own one (parallel issue),
 // or all B <= 2 of them (lane 0 issues; every lane loads the same vector).
 template <int B, bool PAR>
@@ -99,14 +124,16 @@ __device__ __forceinline__ GroupCols<B, PAR> load_group_cols(const int32_t *grou
     return r;
 }
 
-template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT>
+// C: row bytes / 512.  BF16: W and H hold bfloat16 (K = 256 C), else fp32 (K = 128 C).
+template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT, bool BF16 = false>
 __global__ void __launch_bounds__(RING_WARPS * 32, 1)
 sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols,
                   const int32_t *__restrict__ perm, const float *__restrict__ sval,
-                  const float *__restrict__ W, const float *__restrict__ H, float *__restrict__ P,
+                  const void *__restrict__ W, const void *__restrict__ H, float *__restrict__ P,
                   int64_t nnz, int block_groups, unsigned long long *work_counter, int *dev_status)
 {
     using R = RingShape<C>;
+    using PT = typename Piece<BF16>::T;
     constexpr int B = R::B, LPN = R::LPN, F = R::F, NG = RING_NG;
     constexpr bool PAR = R::PAR_ISSUE;
     constexpr int K4 = 32 * C;
@@ -134,7 +161,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     unsigned cons_parity = 0;          // parity of the consumer's current walk
     unsigned in_flight = 0;            // groups issued and not yet consumed
     bool timed_out = false;
-    float4 wc[F];     // this lane's share of the W row of its lane set's current row of S
+    PT wc[F];         // this lane's share of the W row of its lane set's current row of S
     int wc_row = -1;  // that row (-1: none)
     // HAS_HINT: bit 31 of a column index marks a hub column (chosen by the plan so
     // that all hub rows of H fit a share of L2); its copy asks L2 to keep the row,
@@ -187,7 +214,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
         }
     };
     auto load_w = [&](int r) {
-        const float4 *wrow = reinterpret_cast<const float4 *>(W_lane + (size_t)(unsigned)r * R::ROW_BYTES);
+        const PT *wrow = reinterpret_cast<const PT *>(W_lane + (size_t)(unsigned)r * R::ROW_BYTES);
 #pragma unroll
         for (int c = 0; c < F; ++c) wc[c] = __ldg(wrow + c * LPN);
         wc_row = r;
@@ -209,7 +236,24 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
                     c = __ldcs(cols + off + lane);
                     if (HAS_HINT) c &= 0x7fffffff;
                 }
-                const float res = warp_step<32, C, B, false>(W, H, r, c, tail, K4, lane);
+                float res;
+                if constexpr (BF16) {
+                    // every tail nonzero by the whole warp: lane l takes the pieces l, l + 32, ... of both rows
+                    res = 0.f;
+                    for (int j = 0; j < tail; ++j) {
+                        const int rj = __shfl_sync(FULL, r, j), cj = __shfl_sync(FULL, c, j);
+                        const uint4 *w4 = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(W) + (size_t)(unsigned)rj * R::ROW_BYTES);
+                        const uint4 *h4 = reinterpret_cast<const uint4 *>(Hb + (size_t)(unsigned)cj * R::ROW_BYTES);
+                        float a = 0.f;
+                        for (int q = lane; q < R::ROW_BYTES / 16; q += 32) a = Piece<true>::dot(__ldg(w4 + q), __ldg(h4 + q), a);
+#pragma unroll
+                        for (int off2 = 16; off2 >= 1; off2 >>= 1) a += __shfl_xor_sync(FULL, a, off2);
+                        if (lane == j) res = a;
+                    }
+                } else {
+                    res = warp_step<32, C, B, false>(reinterpret_cast<const float *>(W), reinterpret_cast<const float *>(H), r, c,
+                                                     tail, K4, lane);
+                }
                 if (lane < tail) store(off + lane, res);
             }
             continue;
@@ -241,7 +285,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
                 timed_out = true;
                 break;
             }
-            const float4 *srow = reinterpret_cast<const float4 *>(ring + s_cons * R::SLOT_BYTES + g * R::ROW_STRIDE) + l;
+            const PT *srow = reinterpret_cast<const PT *>(ring + s_cons * R::SLOT_BYTES + g * R::ROW_STRIDE) + l;
             --in_flight;
             if (++s_cons == NG) {
                 s_cons = 0;
@@ -249,7 +293,7 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
             }
             float acc = 0.f;
 #pragma unroll
-            for (int c = 0; c < F; ++c) acc = dot4(wc[c], srow[c * LPN], acc);
+            for (int c = 0; c < F; ++c) acc = Piece<BF16>::dot(wc[c], srow[c * LPN], acc);
             // W of the next group, fetched while this group is reduced and stored
             if (r_next != wc_row) load_w(r_next);
             r_next = r_fut;
@@ -273,14 +317,14 @@ sddmm_ring_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ 
     }
 }
 
-template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT>
+template <int C, bool HAS_PERM, bool HAS_SVAL, bool HAS_HINT, bool BF16 = false>
 cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                           const float *W, const float *H, float *P, int64_t nnz, int sm_count,
+                           const void *W, const void *H, float *P, int64_t nnz, int sm_count,
                            unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
     using R = RingShape<C>;
     const size_t smem = (size_t)RING_WARPS * RING_NG * R::SLOT_BYTES + (size_t)RING_WARPS * RING_NG * 8;
-    auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL, HAS_HINT>;
+    auto kern = sddmm_ring_kernel<C, HAS_PERM, HAS_SVAL, HAS_HINT, BF16>;
     static SmemOptinCache optin;  // one opt-in per instantiation and device
     cudaError_t e = optin_dynamic_smem(kern, smem, optin);
     if (e != cudaSuccess) return e;
@@ -297,14 +341,14 @@ cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32
     return cudaGetLastError();
 }
 
-template <int C>
+template <int C, bool BF16 = false>
 cudaError_t launch_ring_t(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
-                          const float *W, const float *H, float *P, int64_t nnz, bool cols_hinted, int sm_count,
+                          const void *W, const void *H, float *P, int64_t nnz, bool cols_hinted, int sm_count,
                           unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
 {
-#define RING_GO(PERM, SVAL, HINT)                                                                                   \
-    return launch_ring_tt<C, PERM, SVAL, HINT>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, \
-                                               stream)
+#define RING_GO(PERM, SVAL, HINT)                                                                                         \
+    return launch_ring_tt<C, PERM, SVAL, HINT, BF16>(rows, cols, perm, sval, W, H, P, nnz, sm_count, work_counter, dev_status, \
+                                                     stream)
 #define RING_GO2(PERM, SVAL)              \
     do {                                  \
         if (cols_hinted) RING_GO(PERM, SVAL, true); \
@@ -337,6 +381,23 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
     case 256: return launch_ring_t<2>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     case 512: return launch_ring_t<4>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     case 1024: return launch_ring_t<8>(rows, cols, perm, sval, W, H, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// bfloat16 operand storage (opt-in): rows of 2K bytes on the same rings, fp32 products and sums.
+bool ring_bf16_supports(int K) { return K == 256 || K == 512 || K == 1024 || K == 2048; }
+
+cudaError_t launch_ring_bf16(const int32_t *rows, const int32_t *cols, const int32_t *perm, const float *sval,
+                             const void *W_bf16, const void *H_bf16, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
+                             unsigned long long *work_counter, int *dev_status, cudaStream_t stream)
+{
+    if (nnz == 0) return cudaSuccess;
+    switch (K) {
+    case 256: return launch_ring_t<1, true>(rows, cols, perm, sval, W_bf16, H_bf16, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 512: return launch_ring_t<2, true>(rows, cols, perm, sval, W_bf16, H_bf16, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 1024: return launch_ring_t<4, true>(rows, cols, perm, sval, W_bf16, H_bf16, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
+    case 2048: return launch_ring_t<8, true>(rows, cols, perm, sval, W_bf16, H_bf16, P, nnz, cols_hinted, sm_count, work_counter, dev_status, stream);
     default: return cudaErrorInvalidValue;
     }
 }

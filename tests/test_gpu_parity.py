@@ -487,6 +487,40 @@ def test_hub_column_hints_do_not_change_results(engine, K, monkeypatch):
     assert_parity(P1, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
 
 
+# ---- opt-in bfloat16 operand storage -----------------------------------------------
+
+@pytest.mark.parametrize("K", [256, 512, 1024, 2048])
+def test_bf16_operand_storage(engine, K):
+    """SDDMM_FLAG_OPERANDS_BF16: W and H stored in bfloat16, products and sums in fp32.  Its oracle is the same
+    CPU loop run on the operands AFTER rounding to bfloat16 (every bfloat16 is an fp32, so the loop is
+    unchanged); with that the usual tolerance applies, 1e-4 max(|ref|, A).  Against the unrounded fp32 operands
+    the results differ by the operands' rounding (2^-9 relative each), which is why the flag is opt-in and
+    outside the fp32 contract."""
+    rng = np.random.default_rng(K)
+    M, N = 700, 600
+    rows, cols = random_coo(rng, M, N, 70_001, empty_rows=[0, 1, 699])
+    vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+    W32 = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda()
+    H32 = torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32)).cuda()
+    W16, H16 = W32.to(torch.bfloat16), H32.to(torch.bfloat16)
+    Wr, Hr = W16.float().cpu().numpy(), H16.float().cpu().numpy()      # what the kernel sees, as fp32
+    for col_tile in (0, 128):
+        plan = engine.plan_coo(M, N, rows, cols, K, 0, col_tile)
+        for sv in (vals, None):
+            P = torch.full((rows.shape[0],), float("nan"), device="cuda")
+            dS = None if sv is None else torch.from_numpy(sv).cuda()
+            plan.execute(W16, H16, P, dS, api.FLAG_OPERANDS_BF16)
+            assert plan.last_kernel_name() == "ring (bf16 operands)"
+            assert_parity(P.cpu().numpy(), rows, cols, Wr, Hr, sv)
+        plan.close()
+    # other K, host arrays or a second kernel flag are refused
+    plan = engine.plan_coo(M, N, rows, cols, 128)
+    with pytest.raises(api.SddmmError) as e:
+        plan.execute(W16, H16, P, None, api.FLAG_OPERANDS_BF16)
+    assert e.value.status == api.K_UNSUPPORTED
+    plan.close()
+
+
 # ---- host operands: pipelined upload / compute / download ----------------------
 
 def test_host_operand_pipeline_matches_unpipelined(monkeypatch):
