@@ -49,7 +49,9 @@ spmm_rows_kernel(const SpmmTask *__restrict__ tasks, int64_t n_tasks, const int6
                  const float *__restrict__ H, float *__restrict__ P_out, float *__restrict__ Y, float *__restrict__ scratch,
                  int K4, unsigned long long *work_counter)
 {
-    constexpr int U = F >= 8 ? 2 : 4;  // nonzeros in flight per warp (register budget: U x F float4 of H per lane)
+    // nonzeros in flight per warp.  Four (two for the longest rows): eight were measured slower at K = 256
+    // (19.6 ms against 16.2 ms on the scale-22 R-MAT matrix) -- the registers they take cost a resident CTA
+    constexpr int U = F >= 8 ? 2 : 4;
     const int lane = threadIdx.x & 31;
     const float4 *H4 = reinterpret_cast<const float4 *>(H);
     bool qv[F];
