@@ -8,10 +8,11 @@
 #include "sddmm_b200.h"
 
 static int failures = 0;
-#define CHECK(cond, what)                                   \
-    do {                                                    \
-        printf("%s: %s\n", (cond) ? "ok" : "FAILED", what); \
-        if (!(cond)) ++failures;                            \
+#define CHECK(cond, what)                                 \
+    do {                                                  \
+        const int holds_ = (cond) ? 1 : 0; /* once */      \
+        printf("%s: %s\n", holds_ ? "ok" : "FAILED", what); \
+        if (!holds_) ++failures;                          \
     } while (0)
 
 int main(int argc, char **argv)

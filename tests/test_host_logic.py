@@ -306,3 +306,37 @@ def test_c_client_of_the_abi(tmp_path):
 def test_shared_memory_optin_cache_is_per_device():
     """A second GPU in the same process must make its own opt-in to large dynamic shared memory."""
     assert api.lib().sddmm_selftest_optin_cache() == api.OK
+
+
+def test_host_code_under_address_and_ub_sanitizers(tmp_path):
+    """The host-only sources (readers, writers, converter, partitioner, generators) compiled with
+    -fsanitize=address,undefined and driven through the C ABI over good, malformed and truncated inputs:
+    any out-of-bounds access, leak of a closed reader or undefined arithmetic ends the run non-zero."""
+    import shutil
+    import subprocess
+    cxx, cc = shutil.which("g++"), shutil.which("gcc")
+    if not cxx or not cc:
+        pytest.skip("no compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "sddmm_gpu_b200", "csrc")
+    san = ["-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer", "-g", "-O1"]
+    objs = []
+    for name in ("mtx_io.cpp", "gen.cpp"):
+        o = str(tmp_path / (name + ".o"))
+        r = subprocess.run([cxx, "-std=c++17", "-I", os.path.join(root, "include"), "-I", src, "-pthread", "-c",
+                            os.path.join(src, name), "-o", o] + san, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        objs.append(o)
+    o = str(tmp_path / "driver.o")
+    r = subprocess.run([cc, "-std=c99", "-D_DEFAULT_SOURCE", "-Wall", "-I", os.path.join(root, "include"), "-c",
+                        os.path.join(root, "tests", "c_abi", "host_sanitize.c"), "-o", o] + san, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    exe = str(tmp_path / "host_sanitize")
+    r = subprocess.run([cxx, o] + objs + ["-o", exe, "-pthread"] + san, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    work = tmp_path / "files"
+    work.mkdir()
+    run = subprocess.run([exe, str(work)], capture_output=True, text=True,
+                         env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1"))
+    assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-3000:]
+    assert "FAILED" not in run.stdout and run.stdout.count("ok:") >= 40
