@@ -64,6 +64,7 @@ def parse_args():
                          "bfloat16-operand SDDMM or of the fused SDDMM->SpMM on the chosen workload (one GPU), one JSON line")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-rebalance", action="store_true", help="N > 1: keep the equal-nonzero row blocks")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
@@ -581,18 +582,19 @@ def main():
         comm = api.Comm(handle, b"\0" * api.COMM_ID_BYTES, 0, 1)
     H_CHUNKS = 8
     dplan = comm.plan_coo(M, N, rows, cols, K, p["panel_rows"], h_chunks=H_CHUNKS)
+
+    def take_shard(dp):
+        a_, b_ = dp.nnz_begin, dp.nnz_end
+        return (a_, b_, dp.row_begin, dp.row_end, (rows[a_:b_] - dp.row_begin).contiguous(), cols[a_:b_].contiguous(),
+                vals[a_:b_].contiguous(), W[dp.row_begin:dp.row_end].contiguous() if world > 1 else W)
+
+    a, b, row_begin, row_end, l_rows, l_cols, l_vals, l_W = take_shard(dplan)
     plan = dplan.local
-    a, b = dplan.nnz_begin, dplan.nnz_end
-    row_begin, row_end = dplan.row_begin, dplan.row_end
-    l_rows = (rows[a:b] - row_begin).contiguous()
-    l_cols = cols[a:b].contiguous()
-    l_vals = vals[a:b].contiguous()
-    l_W = W[row_begin:row_end].contiguous() if world > 1 else W
     rows_host = rows.cpu().numpy() if (world == 1 and not args.no_cpu) else None
     h_bcast_ms = 0.0
     bcast = None
+    rebalance = None
     if world > 1:
-        del W
         if rank != 0:
             H.zero_()  # only rank 0's copy counts; everyone else receives it
         dist.barrier()
@@ -601,6 +603,40 @@ def main():
             dplan.execute(l_W, H, None, l_vals, root=0, flags=api.DIST_BROADCAST_ONLY)   # H arrives in H_CHUNKS pieces
             h_bcast_ms = dplan.last_times()[0]
             dist.barrier()
+        # Equal nonzeros are not equal time: blocks of short rows cost more per nonzero (more W rows, colder
+        # columns).  Measure every rank's nonzeros per millisecond on the equal split, re-cut the rows in
+        # proportion (sddmm_dist_plan_coo_shares), and keep the new split -- part of set-up, like the plan.
+        if not args.no_rebalance:
+            history = []
+            for _ in range(2):
+                Pt = torch.empty(b - a, device=device, dtype=torch.float32)
+                for _ in range(2):
+                    plan.execute(l_W, H, Pt, l_vals, kflag | api.FLAG_ASYNC)
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(4):
+                    plan.execute(l_W, H, Pt, l_vals, kflag | api.FLAG_ASYNC)
+                e1.record()
+                torch.cuda.synchronize()
+                mine = torch.tensor([e0.elapsed_time(e1) / 4, float(b - a)], device=device, dtype=torch.float64)
+                every = [torch.zeros_like(mine) for _ in range(world)]
+                dist.all_gather(every, mine)
+                t_r = np.array([float(x[0].item()) for x in every])
+                n_r = np.array([float(x[1].item()) for x in every])
+                history.append({"rank_ms": [round(x, 4) for x in t_r.tolist()], "rank_nnz": [int(x) for x in n_r.tolist()]})
+                del Pt
+                if t_r.max() / t_r.min() < 1.03:
+                    break
+                shares = n_r / t_r
+                dplan.close()
+                dplan = comm.plan_coo(M, N, rows, cols, K, p["panel_rows"], h_chunks=H_CHUNKS, rank_shares=shares)
+                a, b, row_begin, row_end, l_rows, l_cols, l_vals, l_W = take_shard(dplan)
+                plan = dplan.local
+            rebalance = {"what": "row blocks re-cut in proportion to each rank's measured nonzeros per millisecond",
+                         "rounds": history}
+        del W
     info = plan.info()
     m_nz_local = info.n_nonempty_rows
     n_nz_local = plan.count_cols()
@@ -810,7 +846,7 @@ def main():
                        "parallelism": f"nnz-balanced row blocks x{world}", "kernel": kernel_name,
                        "panel_rows": info.panel_rows, "work_items": info.n_work_items,
                        "plan_ms": info.plan_ms, "h_broadcast_ms": h_bcast_ms,
-                       "rank_ms_per_step": [round(x, 4) for x in rank_ms],
+                       "rank_ms_per_step": [round(x, 4) for x in rank_ms], "rebalance": rebalance,
                        "dense_cells": info.n_dense_cells, "dense_cell_nnz": info.n_dense_nnz,
                        "hub_columns": info.n_hub_cols},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "parity": parity, "h_broadcast": bcast,

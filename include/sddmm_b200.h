@@ -357,6 +357,16 @@ SDDMM_API int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_
                                             int align_rows, double row_cost, int64_t *cuts,
                                             int64_t *nnz_cuts);
 
+/*
+ * The same cuts for unequal parts: part g is to hold shares[g] / sum(shares) of the nonzeros
+ * (shares NULL = equal parts = sddmm_partition_rows).  For row blocks that cost a different
+ * time per nonzero on different GPUs -- e.g. shares proportional to each rank's measured
+ * nonzeros per millisecond.  make_CSC has equal parts only (HiPC18_mpi/util.h:104).
+ */
+SDDMM_API int sddmm_partition_rows_shares(int64_t M, int64_t nnz, const int32_t *rows, int n_parts,
+                                          int align_rows, const double *shares, int64_t *cuts,
+                                          int64_t *nnz_cuts);
+
 /* ---- several GPUs ---------------------------------------------------------------
  *
  * Replaces the MPI program of the reference (HiPC18_mpi/sddmm.cu:139-351, launched as
@@ -402,6 +412,13 @@ SDDMM_API int sddmm_comm_all_gather(sddmm_comm_t c, float *buf, int64_t count_pe
 SDDMM_API int sddmm_dist_plan_coo(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const int32_t *rows,
                                   const int32_t *cols, int K, int panel_rows_hint, int h_chunks, uint32_t flags,
                                   sddmm_dist_plan_t *out);
+/* The same with unequal row blocks: rank r is given rank_shares[r] / sum of the nonzeros
+ * (world entries, identical on every rank; NULL = equal).  Re-plan with shares proportional to
+ * each rank's measured nonzeros per millisecond to even out blocks whose nonzeros cost
+ * different times (short rows cost more per nonzero than long ones). */
+SDDMM_API int sddmm_dist_plan_coo_shares(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const int32_t *rows,
+                                         const int32_t *cols, int K, int panel_rows_hint, int h_chunks,
+                                         const double *rank_shares, uint32_t flags, sddmm_dist_plan_t *out);
 SDDMM_API int sddmm_dist_plan_destroy(sddmm_dist_plan_t p);
 /* The rank's rows [row_begin, row_end) and nonzeros [nnz_begin, nnz_end) of the input, and
  * the number of H chunks in use.  Any output may be NULL. */

@@ -37,7 +37,7 @@ EXPORTED_SYMBOLS = [
     "sddmm_plan_export_tiling", "sddmm_partition_rows", "sddmm_partition_rows_weighted", "sddmm_mtx_open", "sddmm_mtx_read",
     "sddmm_spmm_execute", "sddmm_fused_execute", "sddmm_last_kernel_name", "sddmm_kernel_launches", "sddmm_sync", "sddmm_check_result", "sddmm_selftest_optin_cache",
     "sddmm_comm_unique_id", "sddmm_comm_create", "sddmm_comm_destroy", "sddmm_comm_broadcast", "sddmm_comm_all_gather",
-    "sddmm_dist_plan_coo", "sddmm_dist_plan_destroy", "sddmm_dist_plan_get_shard", "sddmm_dist_plan_local",
+    "sddmm_dist_plan_coo", "sddmm_dist_plan_coo_shares", "sddmm_partition_rows_shares", "sddmm_dist_plan_destroy", "sddmm_dist_plan_get_shard", "sddmm_dist_plan_local",
     "sddmm_dist_execute", "sddmm_dist_last_times", "sddmm_multi_create", "sddmm_multi_destroy", "sddmm_multi_last_error",
     "sddmm_multi_plan_coo", "sddmm_multi_plan_destroy", "sddmm_multi_plan_get_cuts", "sddmm_multi_execute",
     "sddmm_multi_last_kernel_ms",
@@ -101,6 +101,8 @@ def lib():
     L.sddmm_comm_broadcast.argtypes = [vp, vp, i64, C.c_int, vp]
     L.sddmm_comm_all_gather.argtypes = [vp, vp, i64, vp]
     L.sddmm_dist_plan_coo.argtypes = [vp, i64, i64, i64, vp, vp, C.c_int, C.c_int, C.c_int, u32, C.POINTER(vp)]
+    L.sddmm_dist_plan_coo_shares.argtypes = [vp, i64, i64, i64, vp, vp, C.c_int, C.c_int, C.c_int, vp, u32, C.POINTER(vp)]
+    L.sddmm_partition_rows_shares.argtypes = [i64, i64, vp, C.c_int, C.c_int, vp, vp, vp]
     L.sddmm_dist_plan_destroy.argtypes = [vp]
     L.sddmm_dist_plan_get_shard.argtypes = [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64),
                                             C.POINTER(i32)]
@@ -418,15 +420,20 @@ class Comm:
         self.handle._follow_torch_stream(buf)
         self.handle._check(lib().sddmm_comm_all_gather(self._c, _ptr(buf), count_per_rank, cuda_stream))
 
-    def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, h_chunks=1, flags=0):
-        """This rank's part of a plan over the whole matrix (sddmm_dist_plan_coo)."""
+    def plan_coo(self, M, N, rows, cols, K, panel_rows_hint=0, h_chunks=1, flags=0, rank_shares=None):
+        """This rank's part of a plan over the whole matrix (sddmm_dist_plan_coo[_shares]); rank_shares: the
+        fraction of the nonzeros every rank is to get (a sequence of `world` numbers, the same on every rank)."""
         is_dev = _is_cuda_tensor(rows)
         if is_dev:
             flags |= PLAN_DEVICE_INDICES
         p = C.c_void_p()
+        shares = None
+        if rank_shares is not None:
+            shares = np.ascontiguousarray(rank_shares, np.float64)
+            assert shares.shape[0] == self.world
         self.handle._follow_torch_stream(rows, cols)
-        self.handle._check(lib().sddmm_dist_plan_coo(self._c, M, N, int(rows.shape[0]), _ptr(rows), _ptr(cols), K,
-                                                     panel_rows_hint, h_chunks, flags, C.byref(p)))
+        self.handle._check(lib().sddmm_dist_plan_coo_shares(self._c, M, N, int(rows.shape[0]), _ptr(rows), _ptr(cols), K,
+                                                            panel_rows_hint, h_chunks, _ptr(shares), flags, C.byref(p)))
         return DistPlan(self, p, (rows, cols) if is_dev else None)
 
 
@@ -534,6 +541,19 @@ def count_cols_noalloc(d_cols, N, device=0, cuda_stream=None, nnz=None):
 
 
 # ---- host-only helpers (no GPU needed) -------------------------------------
+
+def partition_rows_shares(M, rows, shares, align_rows=1):
+    """Row cuts for parts that are to hold shares[g] / sum(shares) of the nonzeros (sddmm_partition_rows_shares)."""
+    rows = np.ascontiguousarray(rows, np.int32)
+    shares = np.ascontiguousarray(shares, np.float64)
+    n = shares.shape[0]
+    cuts, nnz_cuts = np.zeros(n + 1, np.int64), np.zeros(n + 1, np.int64)
+    st = lib().sddmm_partition_rows_shares(M, rows.shape[0], rows.ctypes.data, n, align_rows, shares.ctypes.data,
+                                           cuts.ctypes.data, nnz_cuts.ctypes.data)
+    if st != OK:
+        raise SddmmError(st)
+    return cuts, nnz_cuts
+
 
 def partition_rows(M, rows, n_parts, align_rows=1, row_cost=0.0):
     rows = np.ascontiguousarray(rows, np.int32)

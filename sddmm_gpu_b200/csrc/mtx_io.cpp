@@ -451,6 +451,40 @@ int sddmm_partition_rows(int64_t M, int64_t nnz, const int32_t *rows, int n_part
     return sddmm_partition_rows_weighted(M, nnz, rows, n_parts, align_rows, 0.0, cuts, nnz_cuts);
 }
 
+int sddmm_partition_rows_shares(int64_t M, int64_t nnz, const int32_t *rows, int n_parts, int align_rows,
+                                const double *shares, int64_t *cuts, int64_t *nnz_cuts)
+{
+    if (!shares) return sddmm_partition_rows(M, nnz, rows, n_parts, align_rows, cuts, nnz_cuts);
+    if (M < 0 || nnz < 0 || n_parts < 1 || !cuts || (nnz > 0 && !rows)) return SDDMM_INVALID_ARG;
+    if (align_rows < 1) align_rows = 1;
+    double total = 0;
+    for (int g = 0; g < n_parts; ++g) {
+        if (!(shares[g] >= 0)) return SDDMM_INVALID_ARG;
+        total += shares[g];
+    }
+    if (!(total > 0)) return SDDMM_INVALID_ARG;
+    cuts[0] = 0;
+    double acc = 0;
+    for (int g = 1; g < n_parts; ++g) {
+        acc += shares[g - 1];
+        int64_t target = (int64_t)((double)nnz * (acc / total));
+        if (target > nnz) target = nnz;
+        int64_t r = target > 0 ? (int64_t)rows[target - 1] + 1 : 0;
+        r = ((r + align_rows - 1) / align_rows) * align_rows;
+        if (r > M) r = M;
+        if (r < cuts[g - 1]) r = cuts[g - 1];
+        cuts[g] = r;
+    }
+    cuts[n_parts] = M;
+    if (nnz_cuts) {
+        for (int g = 0; g <= n_parts; ++g) {
+            const int32_t *lb = std::lower_bound(rows, rows + nnz, cuts[g], [](int32_t a, int64_t b) { return (int64_t)a < b; });
+            nnz_cuts[g] = (int64_t)(lb - rows);
+        }
+    }
+    return SDDMM_OK;
+}
+
 int sddmm_partition_rows_weighted(int64_t M, int64_t nnz, const int32_t *rows, int n_parts, int align_rows,
                                   double row_cost, int64_t *cuts, int64_t *nnz_cuts)
 {

@@ -272,6 +272,13 @@ int sddmm_comm_all_gather(sddmm_comm_t c, float *buf, int64_t count_per_rank, vo
 int sddmm_dist_plan_coo(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const int32_t *rows, const int32_t *cols, int K,
                         int panel_rows_hint, int h_chunks, uint32_t flags, sddmm_dist_plan_t *out)
 {
+    return sddmm_dist_plan_coo_shares(c, M, N, nnz, rows, cols, K, panel_rows_hint, h_chunks, nullptr, flags, out);
+}
+
+int sddmm_dist_plan_coo_shares(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const int32_t *rows, const int32_t *cols, int K,
+                               int panel_rows_hint, int h_chunks, const double *rank_shares, uint32_t flags,
+                               sddmm_dist_plan_t *out)
+{
     if (!c || !out || M < 0 || N < 0 || nnz < 0 || (nnz > 0 && (!rows || !cols))) return SDDMM_INVALID_ARG;
     *out = nullptr;
     sddmm_handle_s *h = c->h;
@@ -306,7 +313,7 @@ int sddmm_dist_plan_coo(sddmm_comm_t c, int64_t M, int64_t N, int64_t nnz, const
         rows_h = host_rows.data();
     }
     if (nnz > 0 && !sddmm_coo_is_row_sorted(nnz, rows_h)) return bail(SDDMM_UNSORTED_INPUT);
-    int st = sddmm_partition_rows(M, nnz, rows_h, c->world, 32, p->cuts.data(), p->nnz_cuts.data());
+    int st = sddmm_partition_rows_shares(M, nnz, rows_h, c->world, 32, rank_shares, p->cuts.data(), p->nnz_cuts.data());
     if (st != SDDMM_OK) return bail(st);
     p->row_begin = p->cuts[c->rank];
     p->row_end = p->cuts[c->rank + 1];
@@ -448,6 +455,8 @@ int sddmm_dist_execute(sddmm_dist_plan_t p, const float *W_local, float *H, cons
     }
     CU_TRY(h, cudaEventRecord(c->ev_bcast_end, cs));
     const sddmm_plan_s *q = p->chunked;
+    // (Leaving SMs free for the broadcast's kernels was tried -- 0, 16 and 32 of 148 -- and changed nothing:
+    // when the broadcast slows down beside the bucket kernels it is for HBM bandwidth, not for SMs.)
     for (int i = 0; i < p->n_chunks; ++i) {
         CU_TRY(h, cudaStreamWaitEvent(s, c->chunk_done[i], 0));
         if (only_bcast || ln == 0) continue;

@@ -7,6 +7,7 @@ import socket
 import sys
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -104,3 +105,26 @@ def test_h_slices_are_assembled_on_every_rank():
     # equal slices take the all-gather, ragged ones a broadcast per slice
     for n_rows in (64, 61):
         mp.spawn(_h_exchange_worker, args=(2, _free_port(), n_rows), nprocs=2, join=True)
+
+
+def test_partition_by_shares():
+    """sddmm_partition_rows_shares: unequal parts, aligned cuts, every nonzero in exactly one part; equal
+    shares give the plain partition; a zero share gives an empty part."""
+    from sddmm_gpu_b200 import api
+    rng = np.random.default_rng(9)
+    M, nnz = 5000, 60_000
+    rows = np.sort(rng.integers(0, M, nnz)).astype(np.int32)
+    cuts, nz = api.partition_rows_shares(M, rows, [1, 1, 1, 1], align_rows=32)
+    c0, n0 = api.partition_rows(M, rows, 4, 32)
+    assert np.array_equal(cuts, c0) and np.array_equal(nz, n0)
+    shares = np.array([4.0, 1.0, 0.0, 3.0])
+    cuts, nz = api.partition_rows_shares(M, rows, shares, align_rows=32)
+    assert cuts[0] == 0 and cuts[-1] == M and nz[0] == 0 and nz[-1] == nnz
+    assert np.all(np.diff(cuts) >= 0) and np.all(cuts[1:-1] % 32 == 0)
+    got = np.diff(nz) / nnz
+    assert np.all(np.abs(got - shares / shares.sum()) < 0.02)        # within a few rows of the target
+    assert nz[2] == nz[3] or got[2] < 0.02                            # the zero share is (nearly) empty
+    for g in range(4):                                                # the cuts and the offsets agree
+        assert np.all((rows[nz[g]:nz[g + 1]] >= cuts[g]) & (rows[nz[g]:nz[g + 1]] < cuts[g + 1]))
+    with pytest.raises(api.SddmmError):
+        api.partition_rows_shares(M, rows, [0.0, 0.0])
