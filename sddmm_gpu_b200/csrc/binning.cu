@@ -580,6 +580,83 @@ cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t
 }
 
 // ---------------------------------------------------------------------------
+// Row groups for the SpMM ring kernel
+// ---------------------------------------------------------------------------
+namespace {
+
+__global__ void group_count_kernel(const int64_t *__restrict__ row_ptr, int64_t M, int B, int64_t *cnt)
+{
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r <= M; r += (int64_t)gridDim.x * blockDim.x)
+        cnt[r] = r < M ? (row_ptr[r + 1] - row_ptr[r] + B - 1) / B : 0;
+}
+__global__ void group_fill_kernel(const int32_t *__restrict__ rows, const int32_t *__restrict__ cols, int64_t nnz,
+                                  const int64_t *__restrict__ row_ptr, const int64_t *__restrict__ gstart, int B,
+                                  int32_t *pcols, int32_t *pidx, int32_t *grow)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t r = rows[i];
+        const int64_t k = i - row_ptr[r];
+        const int64_t g = gstart[r] + k / B;
+        const int64_t pos = g * B + k % B;
+        pcols[pos] = cols[i];
+        pidx[pos] = (int32_t)i;
+        if (k % B == 0) grow[g] = (int32_t)((uint32_t)r | (g + 1 == gstart[r + 1] ? 0x80000000u : 0u));
+    }
+}
+// a padding slot (index -1) repeats the column of its group's first slot, which is always a real nonzero
+__global__ void group_pad_kernel(int32_t *pcols, const int32_t *__restrict__ pidx, int64_t n_slots, int B)
+{
+    for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < n_slots; s += (int64_t)gridDim.x * blockDim.x)
+        if (pidx[s] < 0) pcols[s] = pcols[s / B * B];
+}
+
+}  // namespace
+
+void RowGroups::release()
+{
+    cudaFree(pcols);
+    cudaFree(pidx);
+    cudaFree(grow);
+    pcols = pidx = grow = nullptr;
+    n_groups = 0;
+}
+
+cudaError_t build_row_groups(const int32_t *d_rows, const int32_t *d_cols, const int64_t *d_row_ptr, int64_t nnz, int64_t M,
+                             int B, RowGroups *out, std::vector<int64_t> *gstart_host, cudaStream_t stream)
+{
+    out->release();
+    out->B = B;
+    Scratch cnt, gstart, tmp;
+    CK(cnt.reserve(sizeof(int64_t) * (size_t)(M + 1)));
+    CK(gstart.reserve(sizeof(int64_t) * (size_t)(M + 1)));
+    group_count_kernel<<<grid_for(M + 1), TPB, 0, stream>>>(d_row_ptr, M, B, (int64_t *)cnt.ptr);
+    CK(cudaGetLastError());
+    size_t tb = 0;
+    CK(cub::DeviceScan::ExclusiveSum(nullptr, tb, (const int64_t *)cnt.ptr, (int64_t *)gstart.ptr, (int)(M + 1), stream));
+    CK(tmp.reserve(tb));
+    CK(cub::DeviceScan::ExclusiveSum(tmp.ptr, tb, (const int64_t *)cnt.ptr, (int64_t *)gstart.ptr, (int)(M + 1), stream));
+    gstart_host->resize((size_t)M + 1);
+    CK(cudaMemcpyAsync(gstart_host->data(), gstart.ptr, sizeof(int64_t) * (size_t)(M + 1), cudaMemcpyDeviceToHost, stream));
+    CK(cudaStreamSynchronize(stream));
+    const int64_t G = (*gstart_host)[(size_t)M];
+    if (G * B >= INT32_MAX) return cudaErrorInvalidValue;
+    const size_t slots = (size_t)G * B;
+    CK(cudaMalloc((void **)&out->pcols, sizeof(int32_t) * (slots ? slots : 1)));
+    CK(cudaMalloc((void **)&out->pidx, sizeof(int32_t) * (slots ? slots : 1)));
+    CK(cudaMalloc((void **)&out->grow, sizeof(int32_t) * (size_t)(G ? G : 1)));
+    if (G > 0) {
+        CK(cudaMemsetAsync(out->pidx, 0xff, sizeof(int32_t) * slots, stream));
+        group_fill_kernel<<<grid_for(nnz), TPB, 0, stream>>>(d_rows, d_cols, nnz, d_row_ptr, (const int64_t *)gstart.ptr, B,
+                                                             out->pcols, out->pidx, out->grow);
+        group_pad_kernel<<<grid_for((int64_t)slots), TPB, 0, stream>>>(out->pcols, out->pidx, (int64_t)slots, B);
+        CK(cudaGetLastError());
+    }
+    CK(cudaStreamSynchronize(stream));
+    out->n_groups = G;
+    return cudaSuccess;
+}
+
+// ---------------------------------------------------------------------------
 // Dense-cell classification
 //
 // Three classes of cells, each 128 rows x 64 columns:

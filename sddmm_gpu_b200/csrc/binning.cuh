@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <vector>
+
 #include "common.cuh"
 
 namespace sddmm {
@@ -72,6 +74,21 @@ cudaError_t sort_coo(int32_t *d_a, int32_t *d_b, float *d_v, int64_t nnz, bool t
 cudaError_t build_hub_column_hints(const int32_t *d_cols_p, int64_t nnz, int64_t N, int64_t row_bytes,
                                    int64_t budget_bytes, int32_t *d_cols_hinted, int64_t *n_hub_cols,
                                    int *degree_threshold, cudaStream_t stream);
+
+// Row groups for the SpMM ring kernel: every row's nonzeros cut into groups of B slots (B = rows of H per
+// 4 KB ring slot), the last group of a row padded with slots that repeat the group's first column and carry
+// index -1, so that all B lane sets of a warp always work on the same row of S.
+struct RowGroups {
+    int32_t *pcols = nullptr;  // [n_groups * B] column of every slot
+    int32_t *pidx = nullptr;   // [n_groups * B] input index of the slot's nonzero, -1 for padding
+    int32_t *grow = nullptr;   // [n_groups] row of the group; bit 31 = last group of its row
+    int64_t n_groups = 0;
+    int B = 0;
+    void release();
+};
+// gstart_host receives the first group of every row (M + 1 entries), from which the tasks are built on the host.
+cudaError_t build_row_groups(const int32_t *d_rows, const int32_t *d_cols, const int64_t *d_row_ptr, int64_t nnz, int64_t M,
+                             int B, RowGroups *out, std::vector<int64_t> *gstart_host, cudaStream_t stream);
 
 // Dense-cell classification.  S is cut into cells of DENSE_CELL_ROWS x
 // DENSE_CELL_COLS -- over compacted (nearly) full rows, then compacted (nearly)

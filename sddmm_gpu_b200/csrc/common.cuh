@@ -162,8 +162,19 @@ struct SpmmLongRow {
 };
 bool spmm_supports(int K);  // K a multiple of 4, at most 1024
 // Host: tasks and long-row table from the row pointer over all M rows; *n_slots = scratch slots (K floats each).
+// `budget`: units (nonzeros, or groups when the offsets count groups) a task aims for; 0 = the default.
 void build_spmm_tasks(const int64_t *row_ptr_host, int64_t M, std::vector<SpmmTask> &tasks, std::vector<SpmmLongRow> &long_rows,
-                      int64_t *n_slots);
+                      int64_t *n_slots, int64_t budget = 0);
+cudaError_t launch_spmm_fixup(const SpmmLongRow *long_rows, int64_t n_long, const float *scratch, float *Y, int K,
+                              cudaStream_t stream);
+// The same operations for K = 256, 512, 1024 on the shared-memory gather rings (spmm_ring.cu), over the plan's row
+// groups (build_row_groups); tasks count GROUPS here (j0, j1 are group indices).
+bool spmm_ring_supports(int K);
+int spmm_ring_group_slots(int K);
+cudaError_t launch_spmm_ring(bool fused, const SpmmTask *tasks, int64_t n_tasks, const int32_t *pcols, const int32_t *pidx,
+                             const int32_t *grow, const float *pval, const float *W, const float *H, float *P_out, float *Y,
+                             float *scratch, int K, unsigned long long *work_counter, int *dev_status, int sm_count,
+                             cudaStream_t stream);
 cudaError_t launch_spmm(bool fused, const SpmmTask *tasks, int64_t n_tasks, const SpmmLongRow *long_rows, int64_t n_long,
                         const int64_t *row_ptr, const int32_t *cols, const float *pval, const float *W, const float *H,
                         float *P_out, float *Y, float *scratch, int K, unsigned long long *work_counter, int sm_count,

@@ -104,6 +104,10 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_item_rows_s);
     cudaFree(p->d_used_rows);
     cudaFree(p->d_used_cols);
+    p->row_groups.release();
+    cudaFree(p->d_spmr_tasks);
+    cudaFree(p->d_spmr_long);
+    cudaFree(p->d_spmr_scratch);
     cudaFree(p->d_spmm_tasks);
     cudaFree(p->d_spmm_long);
     cudaFree(p->d_spmm_scratch);
@@ -903,6 +907,37 @@ int ensure_spmm_tasks(sddmm_plan_s *p)
     return SDDMM_OK;
 }
 
+// The ring form's plan data: row groups (device), tasks over groups (host from the groups' row offsets).
+int ensure_spmm_ring(sddmm_plan_s *p)
+{
+    if (p->n_spmr_tasks >= 0) return SDDMM_OK;
+    sddmm_handle_s *h = p->h;
+    std::vector<int64_t> gstart;
+    std::vector<SpmmTask> tasks;
+    std::vector<SpmmLongRow> long_rows;
+    int64_t slots = 0;
+    try {
+        CUDA_TRY(h, build_row_groups(p->d_rows, p->d_cols, p->d_row_ptr, p->nnz, p->M, spmm_ring_group_slots(p->K), &p->row_groups,
+                                     &gstart, h->stream));
+        build_spmm_tasks(gstart.data(), p->M, tasks, long_rows, &slots, /*groups per task*/ 256);
+    } catch (const std::bad_alloc &) {
+        return SDDMM_OUT_OF_MEMORY;
+    }
+    p->device_bytes += (int64_t)(p->row_groups.n_groups * (8 * p->row_groups.B + 4));
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmr_tasks, tasks.size()));
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmr_long, long_rows.size()));
+    CUDA_TRY(h, dev_alloc(p, &p->d_spmr_scratch, (size_t)slots * p->K));
+    if (!tasks.empty())
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_spmr_tasks, tasks.data(), sizeof(SpmmTask) * tasks.size(), cudaMemcpyHostToDevice, h->stream));
+    if (!long_rows.empty())
+        CUDA_TRY(h, cudaMemcpyAsync(p->d_spmr_long, long_rows.data(), sizeof(SpmmLongRow) * long_rows.size(),
+                                    cudaMemcpyHostToDevice, h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    p->n_spmr_tasks = (int64_t)tasks.size();
+    p->n_spmr_long = (int64_t)long_rows.size();
+    return SDDMM_OK;
+}
+
 // Y = P H (fused: P = S o (W H^T) on the fly).  Host arrays are staged for the call.
 int run_spmm(sddmm_plan_s *p, bool fused, const float *W, const float *H, const float *pval, float *P_out, float *Y,
              uint32_t flags)
@@ -912,7 +947,10 @@ int run_spmm(sddmm_plan_s *p, bool fused, const float *W, const float *H, const 
     if (!H || !Y || (fused && !W)) return SDDMM_INVALID_ARG;
     if (flags & ~(uint32_t)SDDMM_FLAG_ASYNC) return SDDMM_INVALID_ARG;
     CUDA_TRY(h, cudaSetDevice(h->device));
-    int st = ensure_spmm_tasks(p);
+    // long rows on the shared-memory rings (SDDMM_SPMM_RING=0: the register-staged kernel for every K)
+    bool ring = spmm_ring_supports(p->K) && p->nnz >= 65536;
+    if (const char *env = std::getenv("SDDMM_SPMM_RING")) ring = ring && std::atoi(env) != 0;
+    int st = ring ? ensure_spmm_ring(p) : ensure_spmm_tasks(p);
     if (st != SDDMM_OK) return st;
     cudaStream_t s = h->stream;
     struct Tmp {
@@ -947,20 +985,27 @@ int run_spmm(sddmm_plan_s *p, bool fused, const float *W, const float *H, const 
         return SDDMM_INVALID_ARG;
     }
     CUDA_TRY(h, cudaEventRecord(h->ev0, s));
-    if (p->M > 0)
+    if (p->M > 0 && ring) {
+        LAUNCH_TRY(h, launch_spmm_ring(fused, p->d_spmr_tasks, p->n_spmr_tasks, p->row_groups.pcols, p->row_groups.pidx,
+                                       p->row_groups.grow, dV, dW, dH, dP, dY, p->d_spmr_scratch, p->K, h->d_work_counter,
+                                       h->d_status, h->sm_count, s));
+        LAUNCH_TRY(h, launch_spmm_fixup(p->d_spmr_long, p->n_spmr_long, p->d_spmr_scratch, dY, p->K, s));
+    } else if (p->M > 0) {
         LAUNCH_TRY(h, launch_spmm(fused, p->d_spmm_tasks, p->n_spmm_tasks, p->d_spmm_long, p->n_spmm_long, p->d_row_ptr, p->d_cols,
                                   dV, dW, dH, dP, dY, p->d_spmm_scratch, p->K, h->d_work_counter, h->sm_count, s));
+    }
     CUDA_TRY(h, cudaEventRecord(h->ev1, s));
-    p->last_kernel = fused ? "fused_sddmm_spmm" : "spmm";
+    p->last_kernel = ring ? (fused ? "fused_sddmm_spmm_ring" : "spmm_ring") : (fused ? "fused_sddmm_spmm" : "spmm");
     if (!y_dev) CUDA_TRY(h, cudaMemcpyAsync(Y, dY, sizeof(float) * mk, cudaMemcpyDeviceToHost, s));
     if (P_out && !p_dev) CUDA_TRY(h, cudaMemcpyAsync(P_out, dP, sizeof(float) * nz, cudaMemcpyDeviceToHost, s));
     if (flags & SDDMM_FLAG_ASYNC) {
         p->last_ms = -1.f;
         return SDDMM_OK;
     }
+    CUDA_TRY(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
     CUDA_TRY(h, cudaStreamSynchronize(s));
     CUDA_TRY(h, cudaEventElapsedTime(&p->last_ms, h->ev0, h->ev1));
-    return SDDMM_OK;
+    return check_device_status(h);
 }
 
 }  // namespace

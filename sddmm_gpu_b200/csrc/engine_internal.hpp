@@ -91,5 +91,11 @@ struct sddmm_plan_s {
     SpmmLongRow *d_spmm_long = nullptr;
     float *d_spmm_scratch = nullptr;
     int64_t n_spmm_tasks = -1, n_spmm_long = 0, n_spmm_slots = 0;
+    // the same for the ring form (K = 256, 512, 1024): padded row groups and tasks counted in groups
+    RowGroups row_groups;
+    SpmmTask *d_spmr_tasks = nullptr;
+    SpmmLongRow *d_spmr_long = nullptr;
+    float *d_spmr_scratch = nullptr;
+    int64_t n_spmr_tasks = -1, n_spmr_long = 0;
 };
 

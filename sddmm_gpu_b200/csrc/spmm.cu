@@ -179,24 +179,25 @@ cudaError_t launch_rows(bool fused, const SpmmTask *tasks, int64_t n_tasks, cons
 }  // namespace
 
 void build_spmm_tasks(const int64_t *row_ptr_host, int64_t M, std::vector<SpmmTask> &tasks, std::vector<SpmmLongRow> &long_rows,
-                      int64_t *n_slots)
+                      int64_t *n_slots, int64_t budget)
 {
+    if (budget <= 0) budget = SPMM_TASK_NNZ;
     tasks.clear();
     long_rows.clear();
     int64_t slots = 0;
     int64_t r = 0;
     while (r < M) {
         const int64_t n = row_ptr_host[r + 1] - row_ptr_host[r];
-        if (n > SPMM_TASK_NNZ) {
-            // a long row: pieces of SPMM_TASK_NNZ nonzeros, one scratch slot each
+        if (n > budget) {
+            // a long row: pieces of `budget` units, one scratch slot each
             SpmmLongRow lr;
             lr.row = (int32_t)r;
             lr.first_slot = (int32_t)slots;
             lr.n_slots = 0;
-            for (int64_t j = row_ptr_host[r]; j < row_ptr_host[r + 1]; j += SPMM_TASK_NNZ) {
+            for (int64_t j = row_ptr_host[r]; j < row_ptr_host[r + 1]; j += budget) {
                 SpmmTask t;
                 t.j0 = j;
-                t.j1 = std::min<int64_t>(j + SPMM_TASK_NNZ, row_ptr_host[r + 1]);
+                t.j1 = std::min<int64_t>(j + budget, row_ptr_host[r + 1]);
                 t.row_a = (int32_t)r;
                 t.row_b = (int32_t)r + 1;
                 t.slot = (int32_t)slots++;
@@ -213,7 +214,7 @@ void build_spmm_tasks(const int64_t *row_ptr_host, int64_t M, std::vector<SpmmTa
         int64_t e = r, acc = 0;
         while (e < M && e - r < 4096) {
             const int64_t ne = row_ptr_host[e + 1] - row_ptr_host[e];
-            if (ne > SPMM_TASK_NNZ || (acc > 0 && acc + ne > SPMM_TASK_NNZ)) break;
+            if (ne > budget || (acc > 0 && acc + ne > budget)) break;
             acc += ne;
             ++e;
         }
@@ -248,11 +249,15 @@ cudaError_t launch_spmm(bool fused, const SpmmTask *tasks, int64_t n_tasks, cons
     else if (F <= 8) e = launch_rows<8>(fused, tasks, n_tasks, row_ptr, cols, pval, W, H, P_out, Y, scratch, K4, work_counter, sm_count, stream);
     else return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
-    if (n_long > 0) {
-        spmm_fixup_kernel<<<(unsigned)std::min<int64_t>(n_long, 4096), 256, 0, stream>>>(long_rows, n_long, scratch, Y, K);
-        e = cudaGetLastError();
-    }
-    return e;
+    return launch_spmm_fixup(long_rows, n_long, scratch, Y, K, stream);
+}
+
+cudaError_t launch_spmm_fixup(const SpmmLongRow *long_rows, int64_t n_long, const float *scratch, float *Y, int K,
+                              cudaStream_t stream)
+{
+    if (n_long <= 0) return cudaSuccess;
+    spmm_fixup_kernel<<<(unsigned)std::min<int64_t>(n_long, 4096), 256, 0, stream>>>(long_rows, n_long, scratch, Y, K);
+    return cudaGetLastError();
 }
 
 }  // namespace sddmm

@@ -59,6 +59,52 @@ def test_spmm_and_fused_every_k(engine, K):
     plan.close()
 
 
+@pytest.mark.parametrize("K", [256, 512, 1024])
+def test_ring_form_for_long_rows(engine, K, monkeypatch):
+    """K = 256, 512, 1024 and 65,536 nonzeros or more run on the shared-memory rings over padded row groups:
+    empty rows at both ends and in the middle (written as zeros), rows of 1 .. B+1 nonzeros (padding), one row
+    holding every column (cut into pieces and summed by the fix-up kernel); against the oracle, and against
+    the register-staged kernel (SDDMM_SPMM_RING=0)."""
+    rng = np.random.default_rng(7 * K)
+    M, N = 900, 700
+    rows, cols = random_coo(rng, M, N, 120_000, empty_rows=[0, 1, 2, 450, 451, 898, 899], hub_row=17)
+    # a few very short rows
+    keep = np.ones(rows.shape[0], bool)
+    for r, n_keep in ((100, 1), (101, 2), (102, 3), (103, 5)):
+        where = np.nonzero(rows == r)[0]
+        keep[where[n_keep:]] = False
+    rows, cols = rows[keep], cols[keep]
+    vals = rng.standard_normal(rows.shape[0]).astype(np.float32)
+    W = rng.standard_normal((M, K)).astype(np.float32)
+    H = rng.standard_normal((N, K)).astype(np.float32)
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    Y = np.full((M, K), np.nan, np.float32)
+    plan.spmm(H, Y, vals)
+    assert plan.last_kernel_name() == "spmm_ring"
+    _check_y(Y, rows, cols, H, M, vals)
+    P_ref = oracle.cpu.sddmm_coo(rows, cols, W, H, vals)
+    P64, A_p = oracle.cpu.sddmm_coo_f64(rows, cols, W, H, vals)
+    _, A_from_p = oracle.cpu.spmm_f64(rows, cols, H, M, A_p)
+    Yf = np.full((M, K), np.nan, np.float32)
+    P_out = np.full(rows.shape[0], np.nan, np.float32)
+    plan.fused(W, H, Yf, vals, P_out)
+    assert plan.last_kernel_name() == "fused_sddmm_spmm_ring"
+    assert np.all(np.abs(P_out.astype(np.float64) - P64) <= TOL * np.maximum(np.abs(P64), A_p))
+    _check_y(Yf, rows, cols, H, M, P_ref, A_extra=A_from_p)
+    Yu = np.full((M, K), np.nan, np.float32)
+    plan.fused(W, H, Yu, None)                       # unscaled
+    _check_y(Yu, rows, cols, H, M, oracle.cpu.sddmm_coo(rows, cols, W, H), A_extra=oracle.cpu.spmm_f64(
+        rows, cols, H, M, oracle.cpu.sddmm_coo_f64(rows, cols, W, H)[1])[1])
+    plan.close()
+    monkeypatch.setenv("SDDMM_SPMM_RING", "0")
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    Y2 = np.full((M, K), np.nan, np.float32)
+    plan.fused(W, H, Y2, vals)
+    assert plan.last_kernel_name() == "fused_sddmm_spmm"
+    _check_y(Y2, rows, cols, H, M, P_ref, A_extra=A_from_p)
+    plan.close()
+
+
 def test_spmm_unsupported_k_and_empty(engine):
     rows, cols = np.array([0, 1], np.int32), np.array([1, 0], np.int32)
     plan = engine.plan_coo(2, 2, rows, cols, 2048)
