@@ -12,7 +12,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libsddmm_b200.so")
+# SDDMM_B200_LIBRARY: another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("SDDMM_B200_LIBRARY") or os.path.join(_HERE, "csrc", "libsddmm_b200.so")
 
 # status codes (include/sddmm_b200.h)
 OK, INVALID_ARG, UNSORTED_INPUT, INDEX_OUT_OF_RANGE, K_UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, \
