@@ -331,10 +331,11 @@ cudaError_t launch_ring_tt(const int32_t *rows, const int32_t *cols, const int32
     e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), stream);
     if (e != cudaSuccess) return e;
     // blocks of groups handed out dynamically: about four blocks per warp on small
-    // inputs, never fewer than 16 groups (the ring drains between blocks) or more than 128
+    // inputs, never fewer than 4 groups (the ring drains between blocks; below ~100 k nonzeros
+    // spreading the work over all warps matters more) or more than 128
     const int64_t n_groups = nnz / R::B;
     int64_t bg = n_groups / ((int64_t)sm_count * RING_WARPS * 4);
-    if (bg < 16) bg = 16;
+    if (bg < 4) bg = 4;
     if (bg > 128) bg = 128;
     kern<<<(unsigned)sm_count, RING_WARPS * 32, smem, stream>>>(rows, cols, perm, sval, W, H, P, nnz, (int)bg,
                                                                 work_counter, dev_status);

@@ -202,7 +202,7 @@ cudaError_t launch_small_tt(const int32_t *rows, const int32_t *cols, const int3
     if (e != cudaSuccess) return e;
     const int64_t n_groups = nnz / R::B;
     int64_t bg = n_groups / ((int64_t)sm_count * SR_WARPS * 4);
-    if (bg < 16) bg = 16;
+    if (bg < 4) bg = 4;
     if (bg > 128) bg = 128;
     kern<<<(unsigned)sm_count, SR_WARPS * 32, smem, stream>>>(rows, cols, perm, sval, W, H, P, nnz, (int)bg, work_counter);
     return cudaGetLastError();
