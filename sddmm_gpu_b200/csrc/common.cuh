@@ -119,6 +119,17 @@ cudaError_t launch_ring(const int32_t *rows, const int32_t *cols, const int32_t 
                         const float *W, const float *H, float *P, int64_t nnz, int K, bool cols_hinted, int sm_count,
                         unsigned long long *work_counter, int *dev_status, cudaStream_t stream);
 
+// Column-tile kernel: a tile of htile_cols(K) rows of H in shared memory, nonzeros in tiled order (column tiles
+// ascending; tile_off[t] = first nonzero of tile t, n_tiles + 1 device entries from build_htile_offsets; perm = input
+// position of a nonzero or null).  htile_cols(K) is 0 for an unsupported K (supported: 128, 256, 512); W and H must
+// be 16-byte aligned.
+int htile_cols(int K);
+cudaError_t build_htile_offsets(const int32_t *cols_t, int64_t nnz, int col_tile, int n_tiles, int64_t *d_off,
+                                cudaStream_t stream);
+cudaError_t launch_htile(const int32_t *rows_t, const int32_t *cols_t, const int32_t *perm, const float *sval, const float *W,
+                         const float *H, float *P, int64_t nnz, int64_t N, int K, int col_tile, const int64_t *tile_off,
+                         int n_tiles, int sm_count, int *dev_status, cudaStream_t stream);
+
 // The same TMA rings over operands stored in bfloat16 (rows of 2K bytes; products and sums in fp32):
 // K = 256, 512, 1024 or 2048.  Opt-in, outside the fp32 tolerance contract.
 bool ring_bf16_supports(int K);

@@ -95,6 +95,10 @@ void free_plan_memory(sddmm_plan_s *p)
     cudaFree(p->d_rows_t);
     cudaFree(p->d_cols_t);
     cudaFree(p->d_perm);
+    cudaFree(p->d_ht_rows);
+    cudaFree(p->d_ht_cols);
+    cudaFree(p->d_ht_perm);
+    cudaFree(p->d_ht_off);
     cudaFree(p->d_row_ptr);
     cudaFree(p->d_items);
     cudaFree(p->d_item_rows);
@@ -397,6 +401,25 @@ int sddmm_plan_coo(sddmm_handle_t h, int64_t M, int64_t N, int64_t nnz, const in
                                             &p->n_hub_cols, &thr, s));
         }
     }
+    // Few columns and many nonzeros per column (a bag-of-words matrix): H is a handful of shared-memory tiles, and
+    // the column-tile kernel reads every H row of a nonzero from shared memory.  Worth it when a CTA's share of
+    // the nonzeros is several times the rows of the tiles it has to load.  SDDMM_HTILE=0 switches it off.
+    {
+        const char *env = std::getenv("SDDMM_HTILE");
+        const int tc = htile_cols(K);
+        const int64_t n_tiles = tc > 0 ? (N + tc - 1) / tc : 0;
+        if (!(env && std::atoi(env) == 0) && tc > 0 && p->n_col_tiles == 1 && p->dense.n_cells == 0 && n_tiles >= 1 &&
+            n_tiles <= 64 && nnz >= 65536 && nnz / h->sm_count >= 8 * (int64_t)tc) {
+            PLAN_TRY(dev_alloc(p, &p->d_ht_perm, (size_t)nnz));
+            PLAN_TRY(dev_alloc(p, &p->d_ht_rows, (size_t)nnz));
+            PLAN_TRY(dev_alloc(p, &p->d_ht_cols, (size_t)nnz));
+            PLAN_TRY(dev_alloc(p, &p->d_ht_off, (size_t)n_tiles + 1));
+            PLAN_TRY(build_tiled_order(p->d_rows, p->d_cols, nnz, N, tc, p->d_ht_perm, p->d_ht_rows, p->d_ht_cols, s));
+            PLAN_TRY(build_htile_offsets(p->d_ht_cols, nnz, tc, (int)n_tiles, p->d_ht_off, s));
+            p->ht_col_tile = tc;
+            p->ht_n_tiles = (int)n_tiles;
+        }
+    }
     // Host-operand pipeline (sddmm_execute with W in host memory): cut S into chunks
     // of consecutive nonzeros, about 128 MB of W rows each, and note the first and
     // last row of every chunk -- rows are sorted, so a chunk needs one contiguous
@@ -678,8 +701,12 @@ int sddmm_execute(sddmm_plan_t p, const float *W, const float *H, const float *S
             h->last_error = "SDDMM_FLAG_TILED_ORDER with S values is not supported on a multi-tile plan";
             return SDDMM_INVALID_ARG;
         }
-        p->last_kernel = use_ring ? ring_name : "panel";
-        if (use_ring)
+        const bool use_htile = p->d_ht_off && !forced && !tiled && ((reinterpret_cast<uintptr_t>(dW) | reinterpret_cast<uintptr_t>(dH)) & 15u) == 0;
+        p->last_kernel = use_htile ? "htile" : use_ring ? ring_name : "panel";
+        if (use_htile)
+            LAUNCH_TRY(h, launch_htile(p->d_ht_rows, p->d_ht_cols, p->d_ht_perm, dS, dW, dH, dP, p->nnz, p->N, p->K, p->ht_col_tile,
+                                       p->d_ht_off, p->ht_n_tiles, h->sm_count, h->d_status, s));
+        else if (use_ring)
             LAUNCH_TRY(h, launch_rows_gather(h, rows_p, p->d_cols_hint ? p->d_cols_hint : cols_p, perm, dS, dW, dH, dP, p->nnz,
                                              p->K, p->d_cols_hint != nullptr, s));
         else

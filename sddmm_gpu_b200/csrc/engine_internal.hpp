@@ -59,6 +59,10 @@ struct sddmm_plan_s {
     int64_t n_items = 0;
     int32_t *d_item_rows = nullptr;  // distinct rows of every item, concatenated
     int32_t *d_cols_hint = nullptr;  // processing-order columns with hub marks (ring kernel), or null
+    // column-tile kernel (few columns, many nonzeros per column): its own tiled order and tile offsets
+    int32_t *d_ht_rows = nullptr, *d_ht_cols = nullptr, *d_ht_perm = nullptr;
+    int64_t *d_ht_off = nullptr;
+    int ht_col_tile = 0, ht_n_tiles = 0;
     // dense cells + row-sorted remainder (single-tile plans of locally dense matrices)
     DensePlan dense;
     WorkItem *d_items_s = nullptr;

@@ -455,6 +455,30 @@ def test_benchmark_configs_default_path(engine, name):
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
 
 
+@pytest.mark.parametrize("K", [128, 256, 512])
+@pytest.mark.parametrize("N", [150, 777, 1500])
+def test_column_tile_kernel(engine, K, N, monkeypatch):
+    # few columns, many nonzeros per column: tiles of H in shared memory (one tile, a ragged last tile, eight tiles
+    # at K = 256); the dense-cell split is switched off so that the 42 % dense case takes this path as well
+    monkeypatch.setenv("SDDMM_DENSE_CELLS", "0")
+    rng = np.random.default_rng(K + N)
+    M = 8000
+    rows, cols = random_coo(rng, M, N, 500_000, empty_rows=(0, 17, M - 1))
+    W = rng.standard_normal((M, K), dtype=np.float32)
+    H = rng.standard_normal((N, K), dtype=np.float32)
+    vals = rng.standard_normal(rows.shape[0], dtype=np.float32)
+    plan = engine.plan_coo(M, N, rows, cols, K)
+    P = np.full(rows.shape[0], np.nan, np.float32)
+    plan.execute(W, H, P, vals, 0)
+    assert plan.last_kernel_name() == "htile"
+    assert_parity(P, rows, cols, W, H, vals)
+    P2 = np.full(rows.shape[0], np.nan, np.float32)
+    plan.execute(W, H, P2, None, api.FLAG_KERNEL_RING)    # the forced ring kernel on the same plan, S = 1
+    assert plan.last_kernel_name().startswith("ring")
+    assert_parity(P2, rows, cols, W, H, None)
+    plan.close()
+
+
 # ---- failure path: a bounded device wait that runs out ------------------------
 
 def test_bounded_wait_reports_timeout_and_handle_survives(engine):
