@@ -310,7 +310,7 @@ def quick_run_fused(handle, p, peak, steps=5, warmup=3):
 
 
 def run_also(handle, device, peak, c4_pattern, args):
-    """The other benchmark configurations and the ends of config 4's K sweep, a few steps each, so that
+    """The other benchmark configurations and config 4's K sweep, a few steps each, so that
     one default run shows every configuration's time and roofline fraction (frac = algorithmic bytes /
     time / measured HBM peak; recomputable from the entry)."""
     from sddmm_gpu_b200 import synth
@@ -339,7 +339,7 @@ def run_also(handle, device, peak, c4_pattern, args):
 
     if c4_pattern is not None:
         rows, cols, vals, M, N = c4_pattern
-        for K in (32, 1024):
+        for K in (32, 64, 128, 512, 1024):   # the K sweep of config 4 (K = 256 is the headline and follows below)
             def make(K=K):
                 g = torch.Generator(device=device)
                 g.manual_seed(synth.SEEDS["c4"] + K)
