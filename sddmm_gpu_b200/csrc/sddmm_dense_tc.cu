@@ -58,9 +58,9 @@ constexpr int STAGES = 3;
 constexpr int A_TILE_BYTES = DR * KC * 4;  // 16 KB
 constexpr int B_TILE_BYTES = DC * KC * 4;  // 8 KB
 constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // head and tail tiles of both operands: 48 KB
-constexpr int CT_STRIDE = DC + 8;          // floats per row of the parked block
+constexpr int CT_STRIDE = DC + 4;          // floats per row of the parked block: the 128-bit stores of eight rows fall into different banks
 constexpr int CT_BYTES = DR * CT_STRIDE * 4;
-constexpr int TC_SMEM_BYTES = STAGES * STAGE_BYTES + CT_BYTES;  // 184,320 bytes
+constexpr int TC_SMEM_BYTES = STAGES * STAGE_BYTES + CT_BYTES;  // 182,272 bytes
 constexpr int N_PRODUCERS = 256, N_EPILOGUE = 512;
 constexpr int MMA_WARP = N_PRODUCERS / 32, EPI_WARP0 = MMA_WARP + 1;
 constexpr int TC_THREADS = N_PRODUCERS + 32 + N_EPILOGUE;  // 800
