@@ -24,15 +24,14 @@
 //               thread), release the accumulator (two of them alternate), park the
 //               block in shared memory and let the cell's nonzeros pick their entries.
 //
-// Shared-memory operand layout (no swizzle, K-major): a tile of R rows x 32 k is a
-// grid of "core matrices" of 8 rows x 16 bytes (four TF32), each stored as 128
-// contiguous bytes; core matrix (row group i = r / 8, k group j = k / 4) sits at
-// (i * 8 + j) * 128 bytes.  The descriptor's leading-dimension offset (between
-// core matrices adjacent in K) is 128 bytes, its stride-dimension offset (between
-// 8-row groups) 1024 bytes; one instruction consumes two core matrices along K,
-// so k-step s starts 256 s bytes into the tile.  Producer thread f writes bytes
-// [16 f, 16 f + 16) of a tile -- conflict-free 128-bit stores -- which is row
-// (f / 64) * 8 + f % 8, k group (f / 8) % 8.
+// Shared-memory operand layout (K-major, 128-byte swizzle): a tile of R rows x 32 k is R lines of
+// 128 bytes, one per row, in groups of eight rows (1024 bytes, the descriptor's stride-dimension
+// offset); inside a group the 16-byte piece c of row r sits at piece c ^ (r % 8) of the row's line --
+// the layout a tile copy with the 128-byte swizzle would produce, and the one the tensor core reads
+// without bank conflicts.  One instruction consumes 32 bytes of every row, so k-step s starts 32 s
+// bytes into the tile.  Producer thread f writes bytes [16 f, 16 f + 16) of a tile, i.e. piece f % 8
+// of row f / 8, which holds the four k from 4 ((f % 8) ^ (f / 8 % 8)) on: the eight lanes of a row
+// read its 128 contiguous bytes in global memory and fill one 128-byte line of shared memory.
 //
 // Every wait is bounded (mbarrier polls with a limit; on expiry the role sets the
 // device status word and leaves its loop, the others run into their own limits),
@@ -65,7 +64,7 @@ constexpr int N_PRODUCERS = 256, N_EPILOGUE = 512;
 constexpr int MMA_WARP = N_PRODUCERS / 32, EPI_WARP0 = MMA_WARP + 1;
 constexpr int TC_THREADS = N_PRODUCERS + 32 + N_EPILOGUE;  // 800
 constexpr uint32_t TMEM_COLS = 2 * DC;  // two accumulators
-constexpr uint32_t LBO = 128, SBO = (KC / 4) * 128;
+constexpr uint32_t LBO = 16, SBO = 8 * KC * 4;  // leading offset unused by swizzled K-major tiles; 8 rows of 128 bytes
 // What the epilogue needs to know about a cell before its product is there: fetched into shared memory two
 // cells ahead.
 constexpr int META_SLOTS = 4;
@@ -76,11 +75,12 @@ struct __align__(16) MetaSlot {
     int32_t pad[3];
 };
 
-// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4), version 1, no swizzle.
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4), version 1,
+// layout type 2 = 128-byte swizzle (bits 61-63).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
 {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // Instruction descriptor of kind::tf32: D = fp32 (bits 4-5 = 1), A = B = TF32 (bits 7-9, 10-12 = 2), both
 // K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24.
@@ -176,7 +176,8 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         // Thread f owns bytes [16 f, 16 f + 16) of every tile, so it only ever reads what it copied itself.
         const int my_cells = (int)((n_cells - blockIdx.x + gridDim.x - 1) / gridDim.x);
         const unsigned total = (unsigned)my_cells * (unsigned)n_chunks;
-        const int kq = ((tid >> 3) & 7) * 4;  // the k group of this thread's pieces: (f >> 3) & 7 with f = tid + 256 i
+        // the k group of this thread's pieces, f = tid + 256 i: piece f % 8 of row f / 8 holds group (f % 8) ^ (f / 8 % 8)
+        const int kq = ((tid & 7) ^ ((tid >> 3) & 7)) * 4;
         // issue cursor: cell, chunk and this thread's operand rows of that cell
         int64_t icell = blockIdx.x;
         int ichunk = 0;
@@ -188,14 +189,14 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int f = tid + i * N_PRODUCERS;
-                int64_t row = (int64_t)dc.row0 + (f >> 6) * 8 + (f & 7);
+                int64_t row = (int64_t)dc.row0 + (f >> 3);
                 if (cls == 0) row = row < n_dense_rows ? dense_rows[row] : M;  // compacted full rows
                 wrow[i] = row < M ? W + row * K + kq : nullptr;
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int f = tid + i * N_PRODUCERS;
-                int64_t col = (int64_t)dc.col0 + (f >> 6) * 8 + (f & 7);
+                int64_t col = (int64_t)dc.col0 + (f >> 3);
                 if (cls == 1) col = col < n_dense_cols ? dense_cols[col] : N;  // compacted full columns
                 hrow[i] = col < N ? H + col * K + kq : nullptr;
             }
@@ -268,7 +269,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES, b_lo = b_hi + B_TILE_BYTES;
 #pragma unroll
                     for (int ks = 0; ks < KC / 8; ++ks) {
-                        const uint32_t o = ks * 256;  // two core matrices along K per instruction
+                        const uint32_t o = ks * 32;  // eight k = 32 bytes of every row per instruction
                         const uint64_t dah = smem_desc(a_hi + o, LBO, SBO), dal = smem_desc(a_lo + o, LBO, SBO);
                         const uint64_t dbh = smem_desc(b_hi + o, LBO, SBO), dbl = smem_desc(b_lo + o, LBO, SBO);
                         mma_tf32_ss(d, dal, dbh, (c > 0 || ks > 0) ? 1u : 0u);  // a cell's very first MMA overwrites
