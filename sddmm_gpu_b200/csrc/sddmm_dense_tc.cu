@@ -124,9 +124,13 @@ __device__ __forceinline__ bool epilogue_all(bool mine)
 }
 __device__ __forceinline__ void epilogue_sync() { asm volatile("barrier.cta.sync 1, 512;" ::: "memory"); }
 
+// A warp waits for a barrier phase: lane 0 polls (32 lanes polling one word cost 32 accesses of the shared-memory
+// pipe per poll), the others take its answer; __shfl_sync orders the warp's memory accesses behind the wait.
 __device__ __forceinline__ bool wait_bar(uint64_t *bar, unsigned parity)
 {
-    return mbar_try_wait(bar, parity) || mbar_wait_bounded(bar, parity);
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = (mbar_try_wait(bar, parity) || mbar_wait_bounded(bar, parity)) ? 1 : 0;
+    return __shfl_sync(FULL, ok, 0) != 0;
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -206,7 +210,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                 if (ichunk == 0) load_rows();
                 const unsigned s = gi % STAGES, use = gi / STAGES;
                 // the MMAs of the stage's previous use are done; one decision per warp
-                if (!__all_sync(FULL, wait_bar(&empty_bar[s], (use & 1u) ^ 1u))) return false;
+                if (!wait_bar(&empty_bar[s], (use & 1u) ^ 1u)) return false;
                 unsigned char *st = smem + s * STAGE_BYTES;
                 const int k0 = ichunk * KC;
                 const bool in_k = k0 + kq < K;  // rows outside the matrix and k beyond K arrive as zeros
@@ -257,12 +261,12 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         for (int64_t cell = blockIdx.x; cell < n_cells && ok; cell += gridDim.x) {
             const unsigned b = n_acc & 1u, use = n_acc >> 1;
             // the epilogue has read this accumulator
-            if (!__all_sync(FULL, wait_bar(&acc_empty[b], (use & 1u) ^ 1u))) { ok = false; break; }
+            if (!wait_bar(&acc_empty[b], (use & 1u) ^ 1u)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t d = tmem + b * DC;
             for (int c = 0; c < n_chunks; ++c) {
                 const unsigned s = g % STAGES;
-                if (!__all_sync(FULL, wait_bar(&full_bar[s], (g / STAGES) & 1u))) { ok = false; break; }
+                if (!wait_bar(&full_bar[s], (g / STAGES) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (lane == 0) {
                     const uint32_t a_hi = smem_u32(smem + s * STAGE_BYTES), a_lo = a_hi + A_TILE_BYTES;
