@@ -332,8 +332,8 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     const unsigned long long mk = m.mask[ew * 8 + u];
                     const unsigned lo = (unsigned)mk, hi = (unsigned)(mk >> 32);
                     const int32_t bs = m.base[ew * 8 + u];
-                    if ((lo >> lane) & 1u) s_lo[u] = __ldcs(sval + bs + __popc(lo & below));
-                    if ((hi >> lane) & 1u) s_hi[u] = __ldcs(sval + bs + __popc(lo) + __popc(hi & below));
+                    if ((lo >> lane) & 1u) s_lo[u] = __ldg(sval + bs + __popc(lo & below));
+                    if ((hi >> lane) & 1u) s_hi[u] = __ldg(sval + bs + __popc(lo) + __popc(hi & below));
                 }
             }
         };
@@ -384,8 +384,8 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     const unsigned lo = (unsigned)mk, hi = (unsigned)(mk >> 32);
                     const int32_t bs = m.base[ew * 8 + u];
                     const float *cr = Ct + (ew * 8 + u) * CT_STRIDE;
-                    if ((lo >> lane) & 1u) __stcs(P + bs + __popc(lo & below), cr[lane] * s_lo[u]);
-                    if ((hi >> lane) & 1u) __stcs(P + bs + __popc(lo) + __popc(hi & below), cr[lane + 32] * s_hi[u]);
+                    if ((lo >> lane) & 1u) P[bs + __popc(lo & below)] = cr[lane] * s_lo[u];
+                    if ((hi >> lane) & 1u) P[bs + __popc(lo) + __popc(hi & below)] = cr[lane + 32] * s_hi[u];
                 }
             } else {
                 // per-nonzero lists, eight nonzeros per thread and trip, the loads of a trip grouped by dependency
