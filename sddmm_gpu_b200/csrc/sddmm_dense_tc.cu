@@ -33,12 +33,18 @@
 // of row f / 8, which holds the four k from 4 ((f % 8) ^ (f / 8 % 8)) on: the eight lanes of a row
 // read its 128 contiguous bytes in global memory and fill one 128-byte line of shared memory.
 //
+// Two forms.  General: every chunk of every cell brings its W and H tiles into one of three stages.  Runs
+// (K <= 64): the CTAs take the cells four consecutive ones at a time, and the W tile (both chunks, head and tail:
+// 64 KB, two buffers alternating) stays in shared memory for as long as the cells that follow belong to the same
+// row block -- only H tiles go through the stages then, and the producers stage and split a third of the bytes.
+//
 // Every wait is bounded (mbarrier polls with a limit; on expiry the role sets the
 // device status word and leaves its loop, the others run into their own limits),
 // the only CTA-wide barriers are at the start and the end, and the TMEM columns
 // are released on every path.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "dense_pick.cuh"
@@ -68,6 +74,13 @@ constexpr uint32_t LBO = 16, SBO = 8 * KC * 4;  // leading offset unused by swiz
 // What the epilogue needs to know about a cell before its product is there: fetched into shared memory two
 // cells ahead.
 constexpr int META_SLOTS = 4;
+// "Runs" form (K <= 64, i.e. at most two chunks): the W tile of a cell stays in shared memory for all the cells of
+// its row block that the CTA takes one after the other (a run); only H tiles go through the stages.
+constexpr int RUN_DEAL = 4;                                   // consecutive cells a CTA takes at a time (2: 0.237 ms, 3: 0.232, 4: 0.227, 8: 0.235, 16: 0.259 on config 5)
+constexpr int A_CHUNK_BYTES = 2 * A_TILE_BYTES;               // head and tail tile of one chunk of W: 32 KB
+constexpr int A_BUF_BYTES = 2 * A_CHUNK_BYTES;                // both chunks: 64 KB, two such buffers alternate
+constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;               // head and tail tile of one chunk of H: 16 KB
+constexpr int RUNS_SMEM_BYTES = 2 * A_BUF_BYTES + STAGES * B_STAGE_BYTES + CT_BYTES;  // 215,040 bytes
 struct __align__(16) MetaSlot {
     unsigned long long mask[DENSE_CELL_ROWS];  // columns held by each cell row
     int32_t base[DENSE_CELL_ROWS];             // input index of each cell row's first nonzero
@@ -133,6 +146,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, unsigned parity)
     return __shfl_sync(FULL, ok, 0) != 0;
 }
 
+template <bool RUNS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, const int32_t *__restrict__ idx,
                       const uint16_t *__restrict__ rc, const unsigned long long *__restrict__ row_mask,
@@ -142,8 +156,11 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                       int64_t N, int K, int *dev_status)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
-    float *Ct = reinterpret_cast<float *>(smem + STAGES * STAGE_BYTES);
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    float *Ct = reinterpret_cast<float *>(smem + (RUNS ? 2 * A_BUF_BYTES + STAGES * B_STAGE_BYTES : STAGES * STAGE_BYTES));
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2], a_empty[2];
+    // runs form: what the MMA warp has to know about chunk g (written by producer thread 0 before its warp arrives on
+    // the chunk's full barrier): bit 0 = W buffer of the chunk's cell, bit 1 = the run ends with this chunk
+    __shared__ uint32_t cinfo[8];
     __shared__ MetaSlot meta[META_SLOTS];
     __shared__ uint32_t tmem_holder;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -156,6 +173,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);            // one tcgen05.commit
             mbar_init(&acc_empty[b], N_EPILOGUE / 32);  // one arrival per epilogue warp, after its tcgen05.ld
+            mbar_init(&a_empty[b], 1);             // one tcgen05.commit after a run's last MMA
         }
         mbar_fence_init();
     }
@@ -171,6 +189,19 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
     const uint32_t tmem = tmem_holder;
     const int n_chunks = (K + KC - 1) / KC;
     bool ok = true;
+    // The cells of this CTA: dealt one at a time, or (runs form) RUN_DEAL consecutive cells of the (row block,
+    // column block)-ordered list at a time; cell_of(i) is the i-th of them.
+    constexpr int DEAL = RUNS ? RUN_DEAL : 1;
+    int my_cells = 0;
+    {
+        const int64_t n_deals = (n_cells + DEAL - 1) / DEAL;
+        if ((int64_t)blockIdx.x < n_deals) {
+            const int64_t mine = (n_deals - blockIdx.x + gridDim.x - 1) / gridDim.x;
+            const int64_t last = blockIdx.x + (mine - 1) * gridDim.x;  // my last deal; the list's last deal may be short
+            my_cells = (int)(mine * DEAL - (last == n_deals - 1 ? n_deals * DEAL - n_cells : 0));
+        }
+    }
+    auto cell_of = [&](int i) -> int64_t { return ((int64_t)(i / DEAL) * gridDim.x + blockIdx.x) * DEAL + i % DEAL; };
 
     if (warp < MMA_WARP) {
         // ---------------- producers ----------------
@@ -178,18 +209,28 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         // element), so it is brought in by 16-byte cp.async copies, two chunks ahead and without holding a
         // register; the tail tile (x minus its TF32 head, exact) is computed from the head tile in shared memory.
         // Thread f owns bytes [16 f, 16 f + 16) of every tile, so it only ever reads what it copied itself.
-        const int my_cells = (int)((n_cells - blockIdx.x + gridDim.x - 1) / gridDim.x);
         const unsigned total = (unsigned)my_cells * (unsigned)n_chunks;
         // the k group of this thread's pieces, f = tid + 256 i: piece f % 8 of row f / 8 holds group (f % 8) ^ (f / 8 % 8)
         const int kq = ((tid & 7) ^ ((tid >> 3) & 7)) * 4;
         // issue cursor: cell, chunk and this thread's operand rows of that cell
-        int64_t icell = blockIdx.x;
+        int icell = 0;  // number of the cell within this CTA
         int ichunk = 0;
+        // runs form: the W tile in shared memory belongs to (row0, compacted or not) = a_key; run_no counts the runs
+        int64_t a_key = -1;
+        int run_no = -1;
+        unsigned carries_a = 0;  // two bits per chunk g % 4: the chunk brought its part of a W tile; into which buffer
         unsigned gi = 0;
         const float *wrow[4], *hrow[2];
+        bool new_run = true;  // the cell at the issue cursor starts a run
         auto load_rows = [&]() {
-            const DenseCell dc = cells[icell];
+            const DenseCell dc = cells[cell_of(icell)];
             const int cls = dc.cls & 0xff;
+            if (RUNS) {
+                const int64_t key = ((int64_t)dc.row0 << 1) | (cls == 0 ? 1 : 0);
+                new_run = key != a_key;
+                a_key = key;
+                if (new_run) ++run_no;
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int f = tid + i * N_PRODUCERS;
@@ -211,23 +252,35 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                 const unsigned s = gi % STAGES, use = gi / STAGES;
                 // the MMAs of the stage's previous use are done; one decision per warp
                 if (!wait_bar(&empty_bar[s], (use & 1u) ^ 1u)) return false;
-                unsigned char *st = smem + s * STAGE_BYTES;
+                // runs form, first chunk of a run: so are the MMAs of the run that used this W buffer before
+                if (RUNS && new_run && ichunk == 0 && run_no >= 2 && !wait_bar(&a_empty[run_no & 1], (((run_no >> 1) - 1) & 1u)))
+                    return false;
+                unsigned char *st_a = RUNS ? smem + (run_no & 1) * A_BUF_BYTES + ichunk * A_CHUNK_BYTES : smem + s * STAGE_BYTES;
+                unsigned char *st_b = RUNS ? smem + 2 * A_BUF_BYTES + s * B_STAGE_BYTES : smem + s * STAGE_BYTES + 2 * A_TILE_BYTES;
                 const int k0 = ichunk * KC;
                 const bool in_k = k0 + kq < K;  // rows outside the matrix and k beyond K arrive as zeros
+                if (!RUNS || new_run) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const bool v = in_k && wrow[i];
-                    cp_async16_zfill(st + (tid + i * N_PRODUCERS) * 16, v ? (const void *)(wrow[i] + k0) : (const void *)W, v ? 16 : 0);
+                    for (int i = 0; i < 4; ++i) {
+                        const bool v = in_k && wrow[i];
+                        cp_async16_zfill(st_a + (tid + i * N_PRODUCERS) * 16, v ? (const void *)(wrow[i] + k0) : (const void *)W, v ? 16 : 0);
+                    }
+                }
+                if (RUNS) {
+                    carries_a = (carries_a & ~(3u << (2 * (gi & 3)))) | (((new_run ? 1u : 0u) | ((unsigned)(run_no & 1) << 1)) << (2 * (gi & 3)));
+                    // bit 0: W buffer; bit 1 (set later, when the next cell is known): the run ends with this chunk
+                    if (tid == 0) cinfo[gi & 7] = (unsigned)(run_no & 1);
+                    // the last chunk of the cell before this one ended a run if this cell starts one
+                    if (tid == 0 && ichunk == 0 && new_run && gi > 0) cinfo[(gi - 1) & 7] |= 2u;
                 }
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     const bool v = in_k && hrow[i];
-                    cp_async16_zfill(st + 2 * A_TILE_BYTES + (tid + i * N_PRODUCERS) * 16,
-                                     v ? (const void *)(hrow[i] + k0) : (const void *)H, v ? 16 : 0);
+                    cp_async16_zfill(st_b + (tid + i * N_PRODUCERS) * 16, v ? (const void *)(hrow[i] + k0) : (const void *)H, v ? 16 : 0);
                 }
                 if (++ichunk == n_chunks) {
                     ichunk = 0;
-                    icell += gridDim.x;
+                    ++icell;
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");  // an empty group past the end keeps the count uniform
@@ -237,16 +290,22 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         ok = issue() && issue();
         for (unsigned g = 0; g < total && ok; ++g) {
             asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's copies of chunk g have landed
-            unsigned char *st = smem + (g % STAGES) * STAGE_BYTES;
+            const unsigned slot = (carries_a >> (2 * (g & 3))) & 3u;
+            unsigned char *st_a = RUNS ? smem + (slot >> 1) * A_BUF_BYTES + (g % (unsigned)n_chunks) * A_CHUNK_BYTES
+                                       : smem + (g % STAGES) * STAGE_BYTES;
+            unsigned char *st_b = RUNS ? smem + 2 * A_BUF_BYTES + (g % STAGES) * B_STAGE_BYTES
+                                       : smem + (g % STAGES) * STAGE_BYTES + 2 * A_TILE_BYTES;
+            if (!RUNS || (slot & 1u)) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int off = (tid + i * N_PRODUCERS) * 16;
-                tail_store(*reinterpret_cast<const float4 *>(st + off), st + A_TILE_BYTES + off);
+                for (int i = 0; i < 4; ++i) {
+                    const int off = (tid + i * N_PRODUCERS) * 16;
+                    tail_store(*reinterpret_cast<const float4 *>(st_a + off), st_a + A_TILE_BYTES + off);
+                }
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int off = (tid + i * N_PRODUCERS) * 16;
-                tail_store(*reinterpret_cast<const float4 *>(st + 2 * A_TILE_BYTES + off), st + 2 * A_TILE_BYTES + B_TILE_BYTES + off);
+                tail_store(*reinterpret_cast<const float4 *>(st_b + off), st_b + B_TILE_BYTES + off);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // my copies and stores -> visible to the tensor core
             __syncwarp();
@@ -258,7 +317,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
     } else if (warp == MMA_WARP) {
         // ---------------- MMA issue: the whole warp walks the loop, lane 0 issues ----------------
         unsigned g = 0, n_acc = 0;
-        for (int64_t cell = blockIdx.x; cell < n_cells && ok; cell += gridDim.x) {
+        for (int i = 0; i < my_cells && ok; ++i) {
             const unsigned b = n_acc & 1u, use = n_acc >> 1;
             // the epilogue has read this accumulator
             if (!wait_bar(&acc_empty[b], (use & 1u) ^ 1u)) { ok = false; break; }
@@ -269,8 +328,11 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                 if (!wait_bar(&full_bar[s], (g / STAGES) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (lane == 0) {
-                    const uint32_t a_hi = smem_u32(smem + s * STAGE_BYTES), a_lo = a_hi + A_TILE_BYTES;
-                    const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES, b_lo = b_hi + B_TILE_BYTES;
+                    const unsigned info = RUNS ? cinfo[g & 7] : 0u;
+                    const uint32_t a_hi = RUNS ? smem_u32(smem + (info & 1u) * A_BUF_BYTES + c * A_CHUNK_BYTES) : smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t a_lo = a_hi + A_TILE_BYTES;
+                    const uint32_t b_hi = RUNS ? smem_u32(smem + 2 * A_BUF_BYTES + s * B_STAGE_BYTES) : a_hi + 2 * A_TILE_BYTES;
+                    const uint32_t b_lo = b_hi + B_TILE_BYTES;
 #pragma unroll
                     for (int ks = 0; ks < KC / 8; ++ks) {
                         const uint32_t o = ks * 32;  // eight k = 32 bytes of every row per instruction
@@ -284,6 +346,11 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                      smem_u32(&empty_bar[s]))
                                  : "memory");
+                    // runs form: the run's W buffer is free once its last MMAs are done
+                    if (RUNS && (info & 2u))
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                         smem_u32(&a_empty[info & 1u]))
+                                     : "memory");
                 }
                 __syncwarp();
                 ++g;
@@ -307,11 +374,10 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         const int quarter = warp & 3, cgroup = ew >> 2;
         const int row = quarter * 32 + lane;
         const unsigned below = (1u << lane) - 1u;
-        const int my_cells = (int)((n_cells - blockIdx.x + gridDim.x - 1) / gridDim.x);
         // metadata of cell i of this CTA -> ring slot i % META_SLOTS, by 16-byte cp.async (97 threads take part)
         auto fetch_meta = [&](int i) {
             if (i < my_cells) {
-                const int64_t c = blockIdx.x + (int64_t)i * gridDim.x;
+                const int64_t c = cell_of(i);
                 MetaSlot &m = meta[i % META_SLOTS];
                 if (et < 64) cp_async16_zfill(&m.mask[et * 2], row_mask + c * DR + et * 2, 16);
                 else if (et < 96) cp_async16_zfill(&m.base[(et - 64) * 4], row_base + c * DR + (et - 64) * 4, 16);
@@ -345,7 +411,7 @@ sddmm_dense_tc_kernel(const DenseCell *__restrict__ cells, int64_t n_cells, cons
         load_s(0, s_lo, s_hi);
         unsigned n_acc = 0;
         for (int i = 0; i < my_cells; ++i) {
-            const int64_t cell = blockIdx.x + (int64_t)i * gridDim.x;
+            const int64_t cell = cell_of(i);
             const MetaSlot &m = meta[i % META_SLOTS];
             const bool masked = (m.cls & 0x100) != 0;
             // two cells ahead: metadata; one cell ahead: S values -- neither depends on the product
@@ -437,14 +503,32 @@ cudaError_t launch_dense_cells_tc(const DenseCell *cells, int64_t n_cells, const
                                   int *dev_status, cudaStream_t stream)
 {
     if (n_cells == 0) return cudaSuccess;
-    static SmemOptinCache optin;  // per device
-    {
-        cudaError_t e = optin_dynamic_smem(sddmm_dense_tc_kernel, TC_SMEM_BYTES, optin);
-        if (e != cudaSuccess) return e;
-    }
     int64_t blocks = sm_count;  // one persistent CTA per SM
     if (blocks > n_cells) blocks = n_cells;
-    sddmm_dense_tc_kernel<<<(unsigned)blocks, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+    // K <= 64: the runs form (the W tile of a row block stays in shared memory across its cells), unless most cells
+    // are cells of compacted full rows / columns -- their operands are shared by thousands of cells and sit in L2, the
+    // staging is not what limits them, and the general form measures faster there (202 M-nonzero attention mask with
+    // 1,311 global rows and columns: 0.839 ms against 0.874 ms; 80 global: 0.246 ms against 0.227 ms).
+    // SDDMM_DENSE_RUNS=0 / 1 forces the general / the runs form.
+    const char *runs_str = getenv("SDDMM_DENSE_RUNS");
+    const int runs_env = runs_str ? atoi(runs_str) : -1;
+    const int64_t compacted = ((n_dense_rows + DR - 1) / DR) * ((N + DC - 1) / DC) + ((n_dense_cols + DC - 1) / DC) * ((M + DR - 1) / DR);
+    const bool runs = runs_env >= 0 ? runs_env != 0 : 2 * compacted < n_cells;
+    if (K <= 2 * KC && runs) {
+        static SmemOptinCache optin_runs;  // per device
+        cudaError_t e = optin_dynamic_smem(sddmm_dense_tc_kernel<true>, RUNS_SMEM_BYTES, optin_runs);
+        if (e != cudaSuccess) return e;
+        sddmm_dense_tc_kernel<true><<<(unsigned)blocks, TC_THREADS, RUNS_SMEM_BYTES, stream>>>(
+            cells, n_cells, idx, rc, row_mask, row_base, dense_rows, n_dense_rows, dense_cols, n_dense_cols, sval, W, H, P, M,
+            N, K, dev_status);
+        return cudaGetLastError();
+    }
+    static SmemOptinCache optin;  // per device
+    {
+        cudaError_t e = optin_dynamic_smem(sddmm_dense_tc_kernel<false>, TC_SMEM_BYTES, optin);
+        if (e != cudaSuccess) return e;
+    }
+    sddmm_dense_tc_kernel<false><<<(unsigned)blocks, TC_THREADS, TC_SMEM_BYTES, stream>>>(
         cells, n_cells, idx, rc, row_mask, row_base, dense_rows, n_dense_rows, dense_cols, n_dense_cols, sval, W, H, P, M, N,
         K, dev_status);
     return cudaGetLastError();

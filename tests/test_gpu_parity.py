@@ -455,6 +455,19 @@ def test_benchmark_configs_default_path(engine, name):
     assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
 
 
+@pytest.mark.parametrize("runs", ["0", "1"])
+@pytest.mark.parametrize("K", [16, 36, 64])
+def test_dense_cell_forms(engine, K, runs, monkeypatch):
+    # K <= 64: the general form of the tcgen05 dense-cell kernel and the one that keeps a row block's W tile in shared
+    # memory across consecutive cells, on a band + global rows / columns mask (compacted and regular cells, runs of
+    # several cells and of one)
+    monkeypatch.setenv("SDDMM_DENSE_RUNS", runs)
+    p = _scaled(synth.attention_mask, M=4096, half_width=96, n_global=20, K=K)
+    P, info = run_plan(engine, p["M"], p["N"], p["rows"], p["cols"], p["W"], p["H"], p["vals"], 0)
+    assert info.n_dense_nnz > 0
+    assert_parity(P, p["rows"], p["cols"], p["W"], p["H"], p["vals"])
+
+
 @pytest.mark.parametrize("K", [128, 256, 512])
 @pytest.mark.parametrize("N", [150, 777, 1500])
 def test_column_tile_kernel(engine, K, N, monkeypatch):
